@@ -71,7 +71,14 @@ class CacheGroup:
         return self.need.window
 
     def bytes_per_page(self, itemsize: int) -> int:
-        return 2 * len(self.entries) * self.need.num_kv_heads * self.page_size * self.need.head_dim * itemsize
+        return (len(self.entries) * self.need.num_kv_heads * self.page_size
+                * (self.need.head_dim + self.need.value_head_dim) * itemsize)
+
+    @property
+    def kept_pages(self) -> int:
+        """Leading pages of a windowed group that are never given back while the request lives:
+        those that hold the positions the window always keeps visible."""
+        return _ceil_div(self.need.keep_first, self.page_size) if self.need.window is not None else 0
 
 
 @dataclass
@@ -117,14 +124,24 @@ class CacheManager:
         self.max_step_tokens = int(max_step_tokens or max_tokens_per_request)
         self.dtype = dtype
         self.device = torch.device(device)
+        # an entry's need: one need, a tuple of needs (at most one of them keys and values), or None
         self.needs = list(needs)
+        self.entry_needs: list[tuple] = [() if need is None else (tuple(need) if isinstance(need, (tuple, list)) else (need,))
+                                         for need in self.needs]
+        for entry, parts in enumerate(self.entry_needs):
+            if sum(isinstance(n, KVCacheNeed) for n in parts) > 1:
+                raise ValueError(f"cache entry {entry} asks for two key/value layouts")
+            names = [n.name for n in parts if isinstance(n, StateNeed)]
+            if len(set(names)) != len(names):
+                raise ValueError(f"cache entry {entry} names a state twice: {names}")
 
         # ---- groups of key/value entries
         self.groups: list[CacheGroup] = []
         self.entry_group: dict[int, tuple[int, int]] = {}   # entry -> (group, index within group)
         by_need: dict[KVCacheNeed, int] = {}
-        for entry, need in enumerate(self.needs):
-            if not isinstance(need, KVCacheNeed):
+        for entry, parts in enumerate(self.entry_needs):
+            need = next((n for n in parts if isinstance(n, KVCacheNeed)), None)
+            if need is None:
                 continue
             if need not in by_need:
                 by_need[need] = len(self.groups)
@@ -142,9 +159,9 @@ class CacheManager:
             group.allocator = PoolAllocator(count, "page")
             group.table = np.full((self.max_requests, self.max_pages_per_request), -1, dtype=np.int32)
             if allocate_device_memory:
-                shape = (len(group.entries), count, group.need.num_kv_heads, self.page_size, group.need.head_dim)
-                group.key = torch.zeros(shape, dtype=dtype, device=self.device)
-                group.value = torch.zeros(shape, dtype=dtype, device=self.device)
+                shape = (len(group.entries), count, group.need.num_kv_heads, self.page_size)
+                group.key = torch.zeros((*shape, group.need.head_dim), dtype=dtype, device=self.device)
+                group.value = torch.zeros((*shape, group.need.value_head_dim), dtype=dtype, device=self.device)
                 if self.device.type == "cuda":
                     group.device_table = torch.full((self.max_requests, self.max_pages_per_request), -1,
                                                     dtype=torch.int32, device=self.device)
@@ -154,11 +171,15 @@ class CacheManager:
 
         # ---- fixed-size state per request
         self.slots = PoolAllocator(self.max_requests, "slot")
-        self.state: dict[int, torch.Tensor] = {}
-        for entry, need in enumerate(self.needs):
-            if isinstance(need, StateNeed) and allocate_device_memory:
-                self.state[entry] = torch.zeros((self.max_requests, *need.shape), dtype=need.dtype,
-                                                device=self.device)
+        self.states: dict[int, dict[str, torch.Tensor]] = {}     # entry -> name -> [slots, ...]
+        self.state: dict[int, torch.Tensor] = {}                 # entry -> the state named "state"
+        for entry, parts in enumerate(self.entry_needs):
+            for need in parts:
+                if isinstance(need, StateNeed) and allocate_device_memory:
+                    tensor = torch.zeros((self.max_requests, *need.shape), dtype=need.dtype, device=self.device)
+                    self.states.setdefault(entry, {})[need.name] = tensor
+                    if need.name == "state":
+                        self.state[entry] = tensor
 
         # ---- slot records (length, last token, counter, temperature, seed): device + host mirror
         self.slot_mirror = np.zeros((self.max_requests, SLOT_WORDS), dtype=np.int32)
@@ -172,6 +193,9 @@ class CacheManager:
             else:
                 self.slot_state = torch.zeros((self.max_requests, SLOT_WORDS), dtype=torch.int32, device=self.device)
 
+        # True: a step that fails leaves every request's fixed-size state as it was (a copy of the
+        # step's slots is taken at begin_step)
+        self.backup_state = True
         self.requests: dict[str, RequestCache] = {}
         self._step: list[tuple[RequestCache, int]] | None = None
         self._state_backup: tuple[torch.Tensor, dict[int, torch.Tensor]] | None = None
@@ -182,7 +206,7 @@ class CacheManager:
         full = _ceil_div(lifetime_tokens, self.page_size)
         if group.window is None:
             return full
-        live = _ceil_div(group.window - 1 + self.max_step_tokens, self.page_size) + 1
+        live = _ceil_div(group.window - 1 + self.max_step_tokens, self.page_size) + 1 + group.kept_pages
         return min(full, live)
 
     def lifetime_pages(self, lifetime_tokens: int) -> tuple[int, ...]:
@@ -231,11 +255,15 @@ class CacheManager:
                                promised=promised,
                                step_new_pages=[[] for _ in self.groups])
         self.requests[request_id] = request
-        for tensor in self.state.values():
+        for tensor in self._state_tensors():
             tensor[slot].zero_()
         self.slot_mirror[slot] = slot_record(temperature=temperature, seed=seed)
         self._new_records.add(slot)
         return request
+
+    def _state_tensors(self):
+        for by_name in self.states.values():
+            yield from by_name.values()
 
     def get(self, request_id: str) -> RequestCache:
         try:
@@ -309,11 +337,11 @@ class CacheManager:
         for request, count in plan:
             request.pending = (request.committed, request.committed + count)
         self._step = plan
-        if self.state:
+        if self.states and self.backup_state:
             # fixed-size state is overwritten in place by the step: keep what an abort must restore
             index = torch.tensor([request.slot for request, _ in plan], dtype=torch.long, device=self.device)
-            self._state_backup = (index, {entry: tensor.index_select(0, index)
-                                          for entry, tensor in self.state.items()})
+            self._state_backup = (index, [(tensor, tensor.index_select(0, index))
+                                          for tensor in self._state_tensors()])
         return [request for request, _ in plan]
 
     def commit_step(self) -> dict[str, dict[int, list[int]]]:
@@ -334,7 +362,9 @@ class CacheManager:
                 first_needed_page = max(0, lowest_needed) // self.page_size
                 pages = request.pages[group.index]
                 gone = []
-                for logical in range(request.first_live[group.index], min(first_needed_page, len(pages))):
+                # the pages of the positions a window keeps visible for good are never given back
+                for logical in range(max(request.first_live[group.index], group.kept_pages),
+                                     min(first_needed_page, len(pages))):
                     if pages[logical] >= 0:
                         gone.append(pages[logical])
                         pages[logical] = -1
@@ -378,8 +408,8 @@ class CacheManager:
             request.pending = None
         if self._state_backup is not None:
             index, saved = self._state_backup
-            for entry, rows in saved.items():
-                self.state[entry].index_copy_(0, index, rows)
+            for tensor, rows in saved:
+                tensor.index_copy_(0, index, rows)
             self._state_backup = None
         self._step = None
 

@@ -15,6 +15,7 @@ from typing import Any, Callable, Mapping
 
 from .qwen2 import Qwen2Config, qwen2_model_spec
 from .spec import ModelSpec
+from .zazasun import ZazasunConfig, zazasun_model_spec
 
 
 @dataclass(frozen=True)
@@ -44,11 +45,14 @@ def known_architectures() -> tuple[str, ...]:
 
 
 def architecture_of(data: Mapping[str, Any]) -> Architecture:
-    """Pick the registry entry that config.json's ``architectures`` names."""
+    """Pick the registry entry that config.json names: the first of ``architectures`` (a list, the
+    Hugging Face convention) or ``architecture`` (one name)."""
     names = data.get("architectures")
+    if names is None and isinstance(data.get("architecture"), str):
+        names = [data["architecture"]]
     if not isinstance(names, (list, tuple)) or not names:
-        raise KeyError("config.json lacks the key 'architectures' (a non-empty list); "
-                       f"known architectures: {', '.join(known_architectures())}")
+        raise KeyError("config.json lacks the key 'architectures' (a non-empty list) or 'architecture' "
+                       f"(a name); known architectures: {', '.join(known_architectures())}")
     name = names[0]
     if name not in _ARCHITECTURES:
         raise KeyError(f"unknown architecture {name!r}; known architectures: "
@@ -76,3 +80,4 @@ def load_config(model_dir: str | Path):
 
 
 register_architecture(Qwen2Config.architecture, Qwen2Config.from_dict, qwen2_model_spec)
+register_architecture(ZazasunConfig.architecture, ZazasunConfig.from_dict, zazasun_model_spec)

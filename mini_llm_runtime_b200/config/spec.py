@@ -30,9 +30,9 @@ class LayerSpec:
 
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None      # None: the layer has no feed-forward
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: PartSpec | None   # None: an arrangement with one norm (both sublayers read it)
     extra_parts: tuple[tuple[str, str, PartSpec], ...] = ()
 
 

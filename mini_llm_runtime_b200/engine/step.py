@@ -81,6 +81,7 @@ class CacheView:
     page_size: int = 0
     window: int | None = None
     state: torch.Tensor | None = None        # [request slots, ...] for a fixed-size-state entry
+    states: dict = field(default_factory=dict)   # every fixed-size state of the entry by name ("state" is ``state``)
     group: int = -1                          # entries of one group share pages, table and ``shared``
     shared: dict = field(default_factory=dict)   # per step and group: mixers may keep derived objects here
 
@@ -361,14 +362,17 @@ class ModelRunner:
         for key, (arrays, counts) in plans.items():
             ctx.plans[key] = ({name: dev[f"plan.{key}.{name}"] for name in arrays}, counts)
         shared_by_group: dict[int, dict] = {group.index: {} for group in cache.groups}
-        for entry, need in enumerate(cache.needs):
+        for entry in range(len(cache.needs)):
             if entry in cache.entry_group:
                 k_pool, v_pool, group = cache.entry_pools(entry)
-                ctx.views[entry] = CacheView(entry, k_pool, v_pool, dev[f"places{group.index}"],
-                                             group.device_table, cache.page_size, group.window,
-                                             group=group.index, shared=shared_by_group[group.index])
+                view = CacheView(entry, k_pool, v_pool, dev[f"places{group.index}"],
+                                 group.device_table, cache.page_size, group.window,
+                                 group=group.index, shared=shared_by_group[group.index])
             else:
-                ctx.views[entry] = CacheView(entry, state=cache.state.get(entry))
+                view = CacheView(entry)
+            view.state = cache.state.get(entry)
+            view.states = cache.states.get(entry, {})
+            ctx.views[entry] = view
         return ctx
 
     # ------------------------------------------------------------------ the step

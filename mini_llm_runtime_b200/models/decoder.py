@@ -31,9 +31,9 @@ class DecoderModel:
                       for name, category, part_spec in layer.extra_parts}
             self.blocks.append(block_cls(
                 build_part("mixer", layer.mixer, compute_dtype),
-                build_part("feed_forward", layer.feed_forward, compute_dtype),
+                None if layer.feed_forward is None else build_part("feed_forward", layer.feed_forward, compute_dtype),
                 build_part("norm", layer.mixer_norm, compute_dtype),
-                build_part("norm", layer.feed_forward_norm, compute_dtype),
+                None if layer.feed_forward_norm is None else build_part("norm", layer.feed_forward_norm, compute_dtype),
                 **({"extras": extras} if extras else {}),
             ))
         self.final_norm = build_part("norm", spec.final_norm, compute_dtype)
@@ -69,11 +69,12 @@ class DecoderModel:
         return self
 
     # ------------------------------------------------------------------ cache
-    def cache_needs(self) -> list[KVCacheNeed | StateNeed | None]:
-        """What each cache entry must hold, taken from the mixer of the run step that writes it."""
-        needs: list[KVCacheNeed | StateNeed | None] = [None] * self.spec.cache_entries
+    def cache_needs(self) -> list:
+        """What each cache entry must hold, taken from the layer of the run step that writes it: a
+        ``KVCacheNeed``, a ``StateNeed``, a tuple of them, or None."""
+        needs: list = [None] * self.spec.cache_entries
         for step in self.spec.run_order:
-            need = self.blocks[step.layer].mixer.cache_need()
+            need = self.blocks[step.layer].cache_need()
             if step.writes_cache:
                 needs[step.cache] = need
             elif needs[step.cache] != need:
@@ -84,7 +85,10 @@ class DecoderModel:
     # ------------------------------------------------------------------ forward
     def forward(self, ctx) -> torch.Tensor:
         """Run the step's rows through the model; float32 logits [wanted rows, vocab]."""
-        residual = self.embedding.forward(ctx.token_ids)
+        if self.embedding.needs_positions:
+            residual = self.embedding.forward(ctx.token_ids, ctx.positions)
+        else:
+            residual = self.embedding.forward(ctx.token_ids)
         pending = None
         for step in self.spec.run_order:
             view = ctx.cache_view(step.cache)

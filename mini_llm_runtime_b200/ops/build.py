@@ -42,6 +42,8 @@ LIBRARIES: dict[str, tuple[str, ...]] = {
     "attention_mma": (),
     "gemm_skinny": (),
     "attention_tcgen05": (),
+    "sequence_mix": (),
+    "attention_diff": (),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -779,6 +779,206 @@ class CudaOps:
             _stream()),
             "decode attention")
 
+    # ------------------------------------------------------------------ 32-bit stream, shifts, recurrences
+    def embedding_positions(self, ids: torch.Tensor, positions: torch.Tensor, table: torch.Tensor,
+                            position_table: torch.Tensor) -> torch.Tensor:
+        """float32 rows table[ids] + position_table[positions]."""
+        _need(ids, "ids", torch.int32, 1)
+        _need(positions, "positions", torch.int32, 1)
+        _need(table, "table", dims=2)
+        _need(position_table, "position_table", table.dtype, 2)
+        if positions.shape[0] != ids.shape[0] or position_table.shape[1] != table.shape[1]:
+            raise KernelError("one position per token id, and tables of equal width")
+        out = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
+        _check(build.load_library("sequence_mix").mlr_embedding_positions(
+            _ptr(ids), _ptr(positions), _ptr(table), _ptr(position_table), _ptr(out), ids.shape[0], table.shape[1],
+            table.shape[0], position_table.shape[0], _code(table.dtype), _stream()), "embedding_positions")
+        return out
+
+    def scalar_rms_norm(self, x: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                        want_float: bool = False):
+        """x * rsqrt(mean(x^2) + eps) * gain for float32 rows and a single gain.  Returns the rows in
+        ``out_dtype``; with ``want_float`` a pair (float32 rows, rows in ``out_dtype``), the same
+        tensor twice when ``out_dtype`` is float32."""
+        _need(x, "x", torch.float32, 2)
+        _need(gain, "gain", torch.float32)
+        if gain.numel() != 1:
+            raise KernelError("the norm's gain is a single number")
+        both = want_float and out_dtype != torch.float32
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        out32 = torch.empty_like(x) if both else None
+        _check(build.load_library("sequence_mix").mlr_scalar_rms_norm(
+            _ptr(x), _ptr(gain), _ptr(out32), _ptr(out), x.shape[0], x.shape[1], ctypes.c_float(eps),
+            _code(out_dtype), _stream()), "scalar_rms_norm")
+        if want_float:
+            return (out32 if both else out), out
+        return out
+
+    def token_shift(self, a: torch.Tensor, coefficients: torch.Tensor, state: torch.Tensor, ctx,
+                    out_dtype: torch.dtype) -> torch.Tensor:
+        """out[i] = a + (previous row of the same request - a) * coefficients[i]; the first row of a
+        segment takes ``state[slot]`` as its previous row, and ``state[slot]`` receives the segment's
+        last row.  a: float32 [rows, width]; coefficients: float32 [n, width]; returns [n, rows, width]."""
+        _need(a, "a", torch.float32, 2)
+        _need(coefficients, "coefficients", torch.float32, 2)
+        _need(state, "state", torch.float32, 2)
+        rows, width = a.shape
+        if coefficients.shape[1] != width or state.shape[1] != width:
+            raise KernelError("coefficients and state rows must have the width of a")
+        n = coefficients.shape[0]
+        out = torch.empty((n, rows, width), dtype=out_dtype, device=a.device)
+        _check(build.load_library("sequence_mix").mlr_token_shift(
+            _ptr(a), _ptr(coefficients), _ptr(state), _ptr(out), _ptr(ctx.seg_q_start), _ptr(ctx.seg_q_len),
+            _ptr(ctx.seg_slot), ctx.num_segments, int(ctx.max_q_len), rows, width, n, _code(out_dtype), _stream()),
+            "token_shift")
+        return out
+
+    @staticmethod
+    def _view(tensor: torch.Tensor, name: str, rows: int, width: int):
+        """A float32 [rows, width] view whose rows may be spaced (a column range of a wider product)."""
+        if (not isinstance(tensor, torch.Tensor) or not tensor.is_cuda or tensor.dtype != torch.float32
+                or tensor.dim() != 2 or tensor.shape != (rows, width) or (width > 1 and tensor.stride(1) != 1)):
+            raise KernelError(f"{name} must be a float32 CUDA view [{rows}, {width}] with unit column stride")
+        return _ptr(tensor), ctypes.c_longlong(tensor.stride(0))
+
+    def _recurrence(self, mode, r, b, v, raw, gate, bias, aux, weight, eps, state, ctx, heads, dim, vdim, out_dtype):
+        rows = r.shape[0]
+        for name, vector, size in (("bias", bias, heads * dim), ("aux", aux, heads * dim),
+                                   ("weight", weight, heads * vdim if mode == 0 else vdim)):
+            _need(vector, name, torch.float32, 1)
+            if vector.shape[0] != size:
+                raise KernelError(f"{name} needs {size} entries, has {vector.shape[0]}")
+        _need(state, "state", torch.float32, 4)
+        if tuple(state.shape[1:]) != (heads, dim, vdim):
+            raise KernelError(f"state has shape {tuple(state.shape)}, expected [slots, {heads}, {dim}, {vdim}]")
+        null = (ctypes.c_void_p(0), ctypes.c_longlong(0))
+        out = torch.empty((rows, heads * vdim), dtype=out_dtype, device=r.device)
+        _check(build.load_library("sequence_mix").mlr_gated_recurrence(
+            mode, *self._view(r, "r", rows, heads * dim), *(null if b is None else self._view(b, "b", rows, heads * dim)),
+            *self._view(v, "v", rows, heads * vdim), *self._view(raw, "raw", rows, heads * dim),
+            *(null if gate is None else self._view(gate, "gate", rows, heads * vdim)),
+            _ptr(bias), _ptr(aux), _ptr(weight), ctypes.c_float(eps), _ptr(state), _ptr(out), _ptr(ctx.seg_q_start),
+            _ptr(ctx.seg_q_len), _ptr(ctx.seg_slot), ctx.num_segments, heads, dim, vdim, _code(out_dtype), _stream()),
+            "gated_recurrence")
+        return out
+
+    def bonus_recurrence(self, r, k, v, decay_raw, gate_raw, decay_bias, bonus, weight, eps, state, ctx,
+                         heads: int, dim: int, out_dtype: torch.dtype) -> torch.Tensor:
+        """Per head, token by token: o = (S + diag(bonus) k v^T)^T r, then S = diag(w) S + k v^T with
+        w = exp(-exp(decay_raw + decay_bias)); the result is o / rms(o) * weight * silu(gate_raw).
+        r, k, v, decay_raw, gate_raw: float32 [rows, heads*dim] views; state: float32
+        [slots, heads, dim, dim], updated in place."""
+        return self._recurrence(0, r, k, v, decay_raw, gate_raw, decay_bias, bonus, weight, eps, state, ctx,
+                                heads, dim, dim, out_dtype)
+
+    def forget_gate_recurrence(self, q_raw, forget_raw, v, forget_bias, lower, weight, eps, state, ctx,
+                               heads: int, dim: int, vdim: int, out_dtype: torch.dtype) -> torch.Tensor:
+        """Per head, token by token: f = lower + (1 - lower) * sigmoid(forget_raw + forget_bias),
+        S = diag(f) S + (1 - f) v^T, o = S^T silu(q_raw); the result is o / rms(o) * weight [vdim]."""
+        return self._recurrence(1, q_raw, None, v, forget_raw, None, forget_bias, lower, weight, eps, state, ctx,
+                                heads, dim, vdim, out_dtype)
+
+    def add_residual(self, residual: torch.Tensor, a: torch.Tensor, b: torch.Tensor | None = None) -> torch.Tensor:
+        """residual += a (+ b), all float32, in place."""
+        _need(residual, "residual", torch.float32)
+        _need(a, "a", torch.float32)
+        if b is not None:
+            _need(b, "b", torch.float32)
+        if a.shape != residual.shape or (b is not None and b.shape != residual.shape):
+            raise KernelError("add_residual needs equal shapes")
+        _check(build.load_library("sequence_mix").mlr_add_residual(
+            _ptr(residual), _ptr(a), _ptr(b), ctypes.c_longlong(residual.numel()), _stream()), "add_residual")
+        return residual
+
+    GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+    def gated_activation(self, gate_up: torch.Tensor, block: int, activation: str) -> torch.Tensor:
+        """act(gate) * up on rows of blocks of ``block`` gate values followed by their up values."""
+        _need(gate_up, "gate_up", dims=2)
+        inner = gate_up.shape[1] // 2
+        if gate_up.shape[1] % 2 or block <= 0 or inner % block:
+            raise KernelError("gate_up rows must hold gate and up blocks of equal width")
+        out = torch.empty((gate_up.shape[0], inner), dtype=gate_up.dtype, device=gate_up.device)
+        _check(build.load_library("sequence_mix").mlr_gated_activation(
+            _ptr(gate_up), _ptr(out), ctypes.c_longlong(gate_up.shape[0]), inner, int(block),
+            self.GATE_ACTIVATIONS[activation], _code(gate_up.dtype), _stream()), "gated_activation")
+        return out
+
+    def linear_gated(self, x: torch.Tensor, weight: torch.Tensor, block: int, activation: str) -> torch.Tensor:
+        """act(x Wg^T) * (x Wu^T) for ``weight`` [2*inner, K] of interleaved gate/up blocks."""
+        if activation == "silu":
+            return self.linear_swiglu(x, weight, block)
+        return self.gated_activation(self.linear(x, weight), block, activation)
+
+    def tanh_(self, x: torch.Tensor) -> torch.Tensor:
+        _need(x, "x")
+        _check(build.load_library("sequence_mix").mlr_tanh_inplace(
+            _ptr(x), ctypes.c_longlong(x.numel()), _code(x.dtype), _stream()), "tanh")
+        return x
+
+    # ------------------------------------------------------------------ differential attention
+    def qk_norm_kv_write(self, qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor, eps: float,
+                         slots: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, heads: int, kv_heads: int,
+                         dim: int, vdim: int, write_kv: bool = True) -> torch.Tensor:
+        """RMS-normalise each (head, map) of q and k over ``dim`` (weights shared by heads and maps),
+        store k and v at ``slots`` of the pools, return q [rows, heads*2*dim] in the pools' dtype.
+        qkv: float32 [rows, 2*heads*dim + 2*kv_heads*dim + kv_heads*vdim]."""
+        _need(qkv, "qkv", torch.float32, 2)
+        _need(q_weight, "q_weight", torch.float32, 1)
+        _need(k_weight, "k_weight", torch.float32, 1)
+        _need(slots, "slots", torch.int64, 1)
+        _need(k_pool, "k_pool", None, 4)
+        _need(v_pool, "v_pool", k_pool.dtype, 4)
+        rows = qkv.shape[0]
+        if qkv.shape[1] != 2 * heads * dim + 2 * kv_heads * dim + kv_heads * vdim:
+            raise KernelError("qkv width does not match the head counts and sizes")
+        if q_weight.shape[0] != dim or k_weight.shape[0] != dim or slots.shape[0] != rows:
+            raise KernelError("norm weights hold dim entries; one slot per row")
+        if (k_pool.shape[1] != kv_heads or k_pool.shape[3] != 2 * dim or v_pool.shape[:3] != k_pool.shape[:3]
+                or v_pool.shape[3] != vdim):
+            raise KernelError(f"pools have shapes {tuple(k_pool.shape)} / {tuple(v_pool.shape)}, expected "
+                              f"[pages, {kv_heads}, page_size, {2 * dim}] / [.., {vdim}]")
+        q = torch.empty((rows, 2 * heads * dim), dtype=k_pool.dtype, device=qkv.device)
+        _check(build.load_library("attention_diff").mlr_qk_norm_kv_write(
+            _ptr(qkv), _ptr(q_weight), _ptr(k_weight), _ptr(slots), _ptr(q), _ptr(k_pool), _ptr(v_pool), rows, heads,
+            kv_heads, dim, vdim, k_pool.shape[2], ctypes.c_float(eps), int(bool(write_kv)), _code(k_pool.dtype),
+            _stream()), "qk_norm_kv_write")
+        return q
+
+    use_diff_decode_kernel = True
+
+    def differential_attention(self, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: AttentionBatch,
+                               heads: int, kv_heads: int, dim: int, vdim: int, scale: float, window: int,
+                               keep_first: int, lam: float, eps: float, out_scale: float) -> torch.Tensor:
+        """Two softmax maps per head over shared values: (a1 - lam * a2) / rms * out_scale.  Key j is
+        visible from position i if j <= i and (i - j < window or j < keep_first); window 0: all."""
+        _need(q, "q", dims=2)
+        _need(k_pool, "k_pool", q.dtype, 4)
+        _need(v_pool, "v_pool", q.dtype, 4)
+        if q.shape[1] != 2 * heads * dim or k_pool.shape[3] != 2 * dim or v_pool.shape[3] != vdim:
+            raise KernelError("q, keys or values do not match the head sizes")
+        if "tile_seg" not in batch.plan:
+            raise KernelError("the batch carries no attention work lists (plan_attention)")
+        out = torch.empty((q.shape[0], heads * vdim), dtype=q.dtype, device=q.device)
+        lib = build.load_library("attention_diff")
+        tail = (heads, kv_heads, dim, vdim, k_pool.shape[2], int(window or 0), int(keep_first), ctypes.c_float(scale),
+                ctypes.c_float(lam), ctypes.c_float(eps), ctypes.c_float(out_scale), _code(q.dtype), _stream())
+        tiles = batch.counts["tiles"]
+        if self.use_diff_decode_kernel and batch.num_decode > 0:
+            listed = None if batch.num_decode == batch.num_segments else batch.plan["decode_seg"]
+            _check(lib.mlr_attention_diff_decode(
+                _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(listed), batch.num_decode,
+                _ptr(batch.seg_q_start), _ptr(batch.seg_pos0), _ptr(batch.block_table), _ptr(batch.seg_slot),
+                batch.block_table.shape[1], *tail), "differential attention (decode)")
+            tiles -= batch.num_decode       # the one-row segments' tiles are the last of the list
+        if tiles > 0:
+            _check(lib.mlr_attention_diff(
+                _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.plan["tile_seg"]),
+                _ptr(batch.plan["tile_row0"]), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0),
+                _ptr(batch.block_table), _ptr(batch.seg_slot), batch.block_table.shape[1], tiles, *tail),
+                "differential attention")
+        return out
+
     # ------------------------------------------------------------------ sampling
     def sample(self, logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch.Tensor,
                counters: torch.Tensor) -> torch.Tensor:

@@ -121,4 +121,84 @@ class GQAAttention(Mixer):
         return k.linear(mixed, self.w_o, self.b_o, residual=residual)
 
 
+class DifferentialAttention(Mixer):
+    """Grouped-query attention with two softmax maps per head over shared values.
+
+    q = Wq x holds, per head, [map 1 | map 2] (2 * dim numbers); k = Wk x likewise per kv head; v = Wv x
+    has ``vdim`` numbers per kv head.  Every (head, map) of q and k is RMS-normalised over ``dim``
+    with a weight shared by all heads and maps; positions do not enter the scores.  Position i sees
+    key j if j <= i and (i - j < window or j < keep_first); window 0 means all earlier keys.  With
+    a1, a2 the maps' outputs and lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff (one number per
+    layer): o = a1 - lambda a2, o / rms(o) * (1 - diff), then Wo.  Scores, softmax and norms are
+    32-bit; the cache holds normalised keys (both maps side by side) and values."""
+
+    graph_safe = True
+    plan_key = "paged_attention"
+
+    def __init__(self, spec, compute_dtype):
+        super().__init__(spec, compute_dtype)
+        a = self.args
+        self.hidden_size = int(a["hidden_size"])
+        self.heads = int(a["heads"])
+        self.kv_heads = int(a.get("kv_heads", self.heads))
+        self.dim = int(a["dim"])
+        self.vdim = int(a["vdim"])
+        self.scale = float(a["scale"])
+        self.diff = float(a["diff"])
+        self.window = int(a.get("window") or 0)
+        self.keep_first = int(a.get("keep_first") or 0) if self.window else 0
+        self.eps = float(a["eps"])
+        if self.heads % self.kv_heads:
+            raise ValueError("heads must be divisible by kv_heads")
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self.lam = 0.0
+
+    def cache_need(self):
+        return KVCacheNeed(self.kv_heads, 2 * self.dim, self.window or None, value_dim=self.vdim,
+                           keep_first=self.keep_first)
+
+    def tensors(self):
+        p, h = self.prefix, self.hidden_size
+        out = {p + "q": TensorSpec((2 * self.heads * self.dim, h)), p + "k": TensorSpec((2 * self.kv_heads * self.dim, h)),
+               p + "v": TensorSpec((self.kv_heads * self.vdim, h)), p + "o": TensorSpec((h, self.heads * self.vdim)),
+               p + "q.norm": TensorSpec((self.dim,), init="norm"), p + "k.norm": TensorSpec((self.dim,), init="norm")}
+        for name in ("lq1", "lk1", "lq2", "lk2"):
+            out[p + name] = TensorSpec((self.dim,), init="bias")
+        return out
+
+    def load(self, tensors, device):
+        p = self.prefix
+        self.w_qkv = self._to_compute(torch.cat([tensors[p + n] for n in "qkv"], dim=0), device)
+        self.w_o = self._to_compute(tensors[p + "o"], device)
+        self.q_norm = tensors[p + "q.norm"].to(device=device, dtype=torch.float32).contiguous()
+        self.k_norm = tensors[p + "k.norm"].to(device=device, dtype=torch.float32).contiguous()
+        l = {n: tensors[p + n].float() for n in ("lq1", "lk1", "lq2", "lk2")}
+        self.lam = float(torch.exp((l["lq1"] * l["lk1"]).sum()) - torch.exp((l["lq2"] * l["lk2"]).sum())) + self.diff
+
+    def step_plan(self, host):
+        return ops.current().plan_attention(host.lengths, host.position_start)
+
+    def _batch(self, ctx, view) -> AttentionBatch:
+        batch = view.shared.get("attention_batch")
+        if batch is None:
+            arrays, counts = ctx.plans.get(self.plan_key, ({}, {}))
+            batch = AttentionBatch(
+                seg_q_start=ctx.seg_q_start, seg_q_len=ctx.seg_q_len, seg_pos0=ctx.seg_pos0, seg_slot=ctx.seg_slot,
+                block_table=view.block_table, num_segments=ctx.num_segments, max_q_len=ctx.max_q_len,
+                max_kv_len=ctx.max_kv_len, plan=arrays, counts=counts)
+            view.shared["attention_batch"] = batch
+        return batch
+
+    def forward(self, x, ctx, view, writes_cache):
+        k = ops.current()
+        qkv = k.linear(x, self.w_qkv, out_dtype=torch.float32)
+        q = k.qk_norm_kv_write(qkv, self.q_norm, self.k_norm, self.eps, view.slots, view.k_pool, view.v_pool,
+                               self.heads, self.kv_heads, self.dim, self.vdim, writes_cache)
+        mixed = k.differential_attention(q, view.k_pool, view.v_pool, self._batch(ctx, view), self.heads,
+                                         self.kv_heads, self.dim, self.vdim, self.scale, self.window,
+                                         self.keep_first, self.lam, self.eps, 1.0 - self.diff)
+        return k.linear(mixed, self.w_o, out_dtype=torch.float32)
+
+
 register_part("mixer", "gqa_attention", GQAAttention)
+register_part("mixer", "differential_attention", DifferentialAttention)

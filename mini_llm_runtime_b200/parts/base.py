@@ -7,6 +7,7 @@ needs, receives them, and computes on the rows of one step.  Five kinds exist:
 * ``feed_forward``     works on each row alone (dense here; experts elsewhere)
 * ``norm``             normalises rows; also offers the fused "add to the residual, then norm"
 * ``position``         position encoding, used by a mixer as a component
+* ``shift``            blends each row with the row of the token before it (carried per request)
 * ``embedding`` / ``head``  token ids to rows, rows to logits
 
 plus ``block``, the arrangement of a layer's parts.  A part never learns which model it is in;
@@ -23,7 +24,7 @@ import torch
 
 from ..config.spec import PartSpec
 
-CATEGORIES = ("mixer", "feed_forward", "norm", "position", "embedding", "head", "block")
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "shift", "embedding", "head", "block")
 
 
 @dataclass(frozen=True)
@@ -31,7 +32,9 @@ class TensorSpec:
     """One checkpoint tensor a part needs.
 
     ``init`` tells the random-weights mode how to fill it: ``matrix`` ~ N(0, 0.02),
-    ``norm`` ~ 1 + N(0, 0.02), ``bias`` ~ N(0, 0.02), ``table`` = integers below ``high``.
+    ``norm`` ~ 1 + N(0, 0.02), ``bias`` ~ N(0, 0.02), ``unit`` ~ U(0, 1), ``table`` = integers below
+    ``high``.  ``flexible`` lists the axes whose size the checkpoint decides (a low-rank
+    bottleneck, say); ``shape`` holds the size the random-weights mode uses there.
     ``storage`` is what the checkpoint stores: ``float`` (bfloat16 unless the checkpoint holds
     32-bit, which is kept) or ``int`` (kept as int32).
     """
@@ -41,23 +44,35 @@ class TensorSpec:
     storage: str = "float"
     high: int = 0
     optional: bool = False
+    flexible: tuple[int, ...] = ()
 
 
 @dataclass(frozen=True)
 class KVCacheNeed:
-    """The mixer wants keys and values of its past positions: all of them, or a window."""
+    """The mixer wants keys and values of its past positions: all of them, or a window.  With a
+    window, the first ``keep_first`` positions stay visible (and cached) for the request's whole
+    life.  ``value_dim`` is the size of a value head where it differs from a key head's."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    value_dim: int | None = None
+    keep_first: int = 0
+
+    @property
+    def value_head_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
 class StateNeed:
-    """The mixer wants a fixed-size tensor per live request (shape without the slot axis)."""
+    """A fixed-size tensor per live request (shape without the slot axis), zero when the request is
+    admitted.  A cache entry may hold several, told apart by ``name``; a part finds them in
+    ``view.states[name]`` (the one called "state" also in ``view.state``)."""
 
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32
+    name: str = "state"
 
 
 class Part:
@@ -172,8 +187,23 @@ class FeedForward(Part):
 
 class Embedding(Part):
     category = "embedding"
+    # True: rows depend on their positions too and the model calls ``forward(token_ids, positions)``
+    needs_positions = False
 
-    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+    def forward(self, token_ids: torch.Tensor, positions: torch.Tensor | None = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Shift(Part):
+    """Blends every row with the row of the same request's previous token; the last row of a step
+    is carried to the next step in a state of the request."""
+
+    category = "shift"
+
+    def state_need(self) -> StateNeed:
+        raise NotImplementedError
+
+    def forward(self, x: torch.Tensor, ctx, view) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -190,8 +220,8 @@ class Block:
 
     category = "block"
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm,
-                 extras: Mapping[str, Part] | None = None):
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward | None, mixer_norm: Norm,
+                 feed_forward_norm: Norm | None, extras: Mapping[str, Part] | None = None):
         self.mixer = mixer
         self.feed_forward = feed_forward
         self.mixer_norm = mixer_norm
@@ -199,7 +229,13 @@ class Block:
         self.extras = dict(extras or {})      # further parts the layer's spec names (``LayerSpec.extra_parts``)
 
     def parts(self) -> tuple[Part, ...]:
-        return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward, *self.extras.values())
+        named = (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward, *self.extras.values())
+        return tuple(part for part in named if part is not None)
+
+    def cache_need(self):
+        """What the layer keeps per request between steps: the mixer's need, or a tuple of needs
+        when the arrangement carries state of its own beside it."""
+        return self.mixer.cache_need()
 
     def finish_load(self, compute_dtype: torch.dtype) -> None:
         """Called once all four parts hold their tensors; an arrangement may fuse across them."""

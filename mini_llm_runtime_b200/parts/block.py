@@ -50,4 +50,29 @@ class PreNormResidual(Block):
         return residual, self.feed_forward.forward(normed, ctx)
 
 
+class ParallelShifted(Block):
+    """One norm, two readers: with h = norm(x) and s = shift(h) (the token shift named ``shift`` among
+    the layer's further parts), x <- x + mixer(s) + feed_forward(h).  The stream x is 32-bit floats
+    and both sublayers hand back 32-bit rows, so the sum is taken in 32-bit and rounded once.  A layer
+    without a feed-forward adds the mixer's output alone.  The shift's carried row is a state of the
+    layer beside whatever the mixer keeps."""
+
+    def cache_need(self):
+        own = self.mixer.cache_need()
+        own = () if own is None else (tuple(own) if isinstance(own, (tuple, list)) else (own,))
+        return (*own, self.extras["shift"].state_need())
+
+    def forward(self, residual, pending, ctx, view, writes_cache):
+        kernels = ops.current()
+        if pending is not None:
+            residual = kernels.add_residual(residual, pending)
+        h32, h = self.mixer_norm.forward_both(residual)
+        wants_float = getattr(self.mixer, "wants_float_input", False)
+        shifted = self.extras["shift"].forward(h32, ctx, view, torch.float32 if wants_float else None)[0]
+        mixed = self.mixer.forward(shifted, ctx, view, writes_cache)
+        passed = None if self.feed_forward is None else self.feed_forward.forward(h, ctx)
+        return kernels.add_residual(residual, mixed, passed), None
+
+
 register_part("block", "pre_norm_residual", PreNormResidual)
+register_part("block", "parallel_shifted", ParallelShifted)

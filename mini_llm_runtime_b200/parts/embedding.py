@@ -29,7 +29,7 @@ class TokenEmbedding(Embedding):
     def load(self, tensors, device):
         self.weight = self._to_compute(tensors[self.prefix + "weight"], device)
 
-    def forward(self, token_ids):
+    def forward(self, token_ids, positions=None):
         return ops.current().embedding(token_ids, self.weight)
 
 
@@ -64,24 +64,59 @@ class TiedHead(Head):
 
 
 class LinearHead(Head):
+    """logits = x H^T with the head's own matrix: ``<prefix>weight``, or the checkpoint name the
+    spec gives as ``tensor``."""
+
     graph_safe = True
 
     def __init__(self, spec, compute_dtype):
         super().__init__(spec, compute_dtype)
         self.vocab_size = int(self.args["vocab_size"])
         self.hidden_size = int(self.args["hidden_size"])
+        self.tensor = self.args.get("tensor") or self.prefix + "weight"
         self.weight: torch.Tensor | None = None
 
     def tensors(self):
-        return {self.prefix + "weight": TensorSpec((self.vocab_size, self.hidden_size))}
+        return {self.tensor: TensorSpec((self.vocab_size, self.hidden_size))}
 
     def load(self, tensors, device):
-        self.weight = self._to_compute(tensors[self.prefix + "weight"], device)
+        self.weight = self._to_compute(tensors[self.tensor], device)
 
     def forward(self, x, embedding):
         return ops.current().linear(x, self.weight, None, out_dtype=torch.float32)
 
 
+class TokenPositionEmbedding(Embedding):
+    """row = E[token] + P[position]: a learned vector per position, added unscaled.  The sum is
+    taken and handed on in 32-bit floats (the model's residual stream is 32-bit), whatever the
+    compute dtype.  Checkpoint names come from the spec (``token_tensor``, ``position_tensor``)."""
+
+    graph_safe = True
+    needs_positions = True
+
+    def __init__(self, spec, compute_dtype):
+        super().__init__(spec, compute_dtype)
+        self.vocab_size = int(self.args["vocab_size"])
+        self.hidden_size = int(self.args["hidden_size"])
+        self.max_positions = int(self.args["max_positions"])
+        self.token_tensor = self.args.get("token_tensor") or self.prefix + "weight"
+        self.position_tensor = self.args.get("position_tensor") or self.prefix + "positions"
+        self.weight: torch.Tensor | None = None
+        self.positions: torch.Tensor | None = None
+
+    def tensors(self):
+        return {self.token_tensor: TensorSpec((self.vocab_size, self.hidden_size)),
+                self.position_tensor: TensorSpec((self.max_positions, self.hidden_size))}
+
+    def load(self, tensors, device):
+        self.weight = self._to_compute(tensors[self.token_tensor], device)
+        self.positions = self._to_compute(tensors[self.position_tensor], device)
+
+    def forward(self, token_ids, positions=None):
+        return ops.current().embedding_positions(token_ids, positions, self.weight, self.positions)
+
+
 register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("embedding", "token_position_embedding", TokenPositionEmbedding)
 register_part("head", "tied_head", TiedHead)
 register_part("head", "linear_head", LinearHead)

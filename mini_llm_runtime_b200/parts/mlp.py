@@ -57,4 +57,47 @@ class SwiGLU(FeedForward):
         return k.linear(hidden, self.w_down, residual=residual)
 
 
+class GatedMLP(FeedForward):
+    """down(act(gate(x)) * up(x)) without biases, ``activation`` being ``silu`` or ``gelu_tanh``
+    (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).  The result leaves in 32-bit floats, for
+    arrangements that sum into a 32-bit stream.  ``names`` gives the three checkpoint names after
+    the prefix.  gate and up are stacked like SwiGLU's."""
+
+    graph_safe = True
+
+    def __init__(self, spec, compute_dtype):
+        super().__init__(spec, compute_dtype)
+        self.hidden_size = int(self.args["hidden_size"])
+        self.intermediate_size = int(self.args["intermediate_size"])
+        self.activation = str(self.args.get("activation", "silu"))
+        if self.activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"unknown gate activation {self.activation!r}")
+        self.names = tuple(self.args.get("names") or ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
+        self.w_gate_up = self.w_down = None
+        self.block = self.intermediate_size
+
+    def tensors(self):
+        gate, up, down = (self.prefix + name for name in self.names)
+        return {gate: TensorSpec((self.intermediate_size, self.hidden_size)),
+                up: TensorSpec((self.intermediate_size, self.hidden_size)),
+                down: TensorSpec((self.hidden_size, self.intermediate_size))}
+
+    def load(self, tensors, device):
+        gate, up, down = (tensors[self.prefix + name] for name in self.names)
+        if self.intermediate_size % 64 == 0:
+            self.block = 64
+            stacked = torch.cat([gate.view(-1, 64, self.hidden_size), up.view(-1, 64, self.hidden_size)], dim=1)
+            stacked = stacked.reshape(2 * self.intermediate_size, self.hidden_size)
+        else:
+            stacked = torch.cat([gate, up], dim=0)
+        self.w_gate_up = self._to_compute(stacked, device)
+        self.w_down = self._to_compute(down, device)
+
+    def forward(self, x, ctx):
+        k = ops.current()
+        hidden = k.linear_gated(x, self.w_gate_up, self.block, self.activation)
+        return k.linear(hidden, self.w_down, out_dtype=torch.float32)
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "gated_mlp", GatedMLP)

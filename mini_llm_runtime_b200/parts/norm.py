@@ -38,4 +38,32 @@ class RMSNorm(Norm):
         return ops.current().add_rms_norm(residual, delta, None if self.folded else self.weight, self.eps)
 
 
+class ScalarRMSNorm(Norm):
+    """y = x * rsqrt(mean(x^2) + eps) * g with a single learned number g for the whole row.  It reads
+    a 32-bit residual stream and hands out rows in the compute dtype (``forward``), or both those and
+    the 32-bit rows (``forward_both``) for what continues in 32-bit.  The checkpoint tensor (a scalar)
+    is named by the spec (``tensor``)."""
+
+    graph_safe = True
+
+    def __init__(self, spec, compute_dtype):
+        super().__init__(spec, compute_dtype)
+        self.eps = float(self.args["eps"])
+        self.tensor = self.args.get("tensor") or self.prefix + "weight"
+        self.gain: torch.Tensor | None = None
+
+    def tensors(self):
+        return {self.tensor: TensorSpec((), init="norm")}
+
+    def load(self, tensors, device):
+        self.gain = tensors[self.tensor].to(device=device, dtype=torch.float32).reshape(1).contiguous()
+
+    def forward(self, x):
+        return ops.current().scalar_rms_norm(x, self.gain, self.eps, self.compute_dtype)
+
+    def forward_both(self, x):
+        return ops.current().scalar_rms_norm(x, self.gain, self.eps, self.compute_dtype, want_float=True)
+
+
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "scalar_rms_norm", ScalarRMSNorm)

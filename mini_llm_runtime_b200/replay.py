@@ -39,7 +39,7 @@ def parse_args(argv=None) -> argparse.Namespace:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at any time (pool size)")
     parser.add_argument("--block-size", type=int, default=16, help="tokens per cache page (default 16)")
-    parser.add_argument("--max-requests", type=int, default=8, help="request slots (default 8)")
+    parser.add_argument("--max-requests", type=int, default=4, help="request slots: the most requests live at once (default 4)")
     parser.add_argument("--device", default="cuda:0")
     return parser.parse_args(argv)
 

@@ -97,7 +97,10 @@ def check_tensors(expected: Mapping[str, "TensorSpec"], found: Mapping[str, torc
         if name not in found:
             continue
         tensor = found[name]
-        if tuple(tensor.shape) != tuple(spec.shape):
+        flexible = getattr(spec, "flexible", ())
+        fits = len(tensor.shape) == len(spec.shape) and all(
+            axis in flexible or got == want for axis, (got, want) in enumerate(zip(tensor.shape, spec.shape)))
+        if not fits:
             wrong_shape.append((name, tuple(tensor.shape), tuple(spec.shape)))
         is_int = not tensor.dtype.is_floating_point
         if (spec.storage == "int") != is_int:

@@ -3,7 +3,7 @@ result as a model folder (config.json + model.safetensors) that the ordinary loa
 
 The reference has no such mode; its tests draw a tiny state dict from a seeded generator
 (tests/test_qwen_weights.py:25-65 there).  Distributions: matrices ~ N(0, 0.02), norm weights
-~ 1 + N(0, 0.02), biases ~ N(0, 0.02), integer tables uniform below their bound.  Tensors are
+~ 1 + N(0, 0.02), biases ~ N(0, 0.02), blend coefficients and lower bounds ~ U(0, 1), integer tables uniform below their bound.  Tensors are
 drawn one by one in sorted-name order from one CPU generator, in float32, then rounded to the
 storage dtype, so a given (configuration, seed, dtype) always yields the same bytes.  For models
 of many gigabytes ``device=`` draws from that device's generator instead (other bytes, the same
@@ -38,6 +38,9 @@ def random_tensors(expected: Mapping[str, "TensorSpec"], seed: int,
         if spec.storage == "int" or spec.init == "table":
             tensors[name] = torch.randint(0, max(int(spec.high), 1), shape, generator=generator,
                                           dtype=torch.int32, device=device)
+            continue
+        if spec.init == "unit":
+            tensors[name] = torch.rand(shape, generator=generator, dtype=torch.float32, device=device).to(dtype)
             continue
         values = torch.randn(shape, generator=generator, dtype=torch.float32, device=device) * STD
         if spec.init == "norm":

@@ -185,3 +185,109 @@ class FakeOps:
                 u = uniform_from_seed(int(seeds[row]) & ((1 << 64) - 1), int(counters[row]))
                 tokens[row] = temperature_sample(logits[row], temperature, u)[0]
         return tokens
+
+    # ---- the kernels of 32-bit-stream models with shifts, recurrences and differential attention
+    def embedding_positions(self, ids, positions, table, position_table):
+        return table[ids.long()].float() + position_table[positions.long()].float()
+
+    def scalar_rms_norm(self, x, gain, eps, out_dtype, want_float=False):
+        out = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * gain
+        return (out, out.to(out_dtype)) if want_float else out.to(out_dtype)
+
+    def token_shift(self, a, coefficients, state, ctx, out_dtype):
+        out = torch.empty((coefficients.shape[0], *a.shape), dtype=torch.float32)
+        for segment in ctx.segments:
+            rows = slice(segment.row_start, segment.row_start + segment.length)
+            previous = torch.cat([state[segment.slot][None], a[rows][:-1]], dim=0)
+            out[:, rows] = a[rows][None] + (previous - a[rows])[None] * coefficients[:, None, :]
+            state[segment.slot] = a[rows][-1]
+        return out.to(out_dtype)
+
+    def bonus_recurrence(self, r, k, v, decay_raw, gate_raw, decay_bias, bonus, weight, eps, state, ctx, heads, dim,
+                         out_dtype):
+        out = torch.empty((r.shape[0], heads * dim), dtype=torch.float32)
+        w = torch.exp(-torch.exp(decay_raw + decay_bias))
+        u = bonus.view(heads, dim)
+        for segment in ctx.segments:
+            S = state[segment.slot]
+            for row in range(segment.row_start, segment.row_start + segment.length):
+                kv = k[row].view(heads, dim, 1) * v[row].view(heads, 1, dim)
+                o = torch.einsum("hi,hij->hj", r[row].view(heads, dim), S + u[:, :, None] * kv)
+                S = w[row].view(heads, dim, 1) * S + kv
+                o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps)
+                out[row] = o.reshape(-1) * weight * torch.nn.functional.silu(gate_raw[row])
+            state[segment.slot] = S
+        return out.to(out_dtype)
+
+    def forget_gate_recurrence(self, q_raw, forget_raw, v, forget_bias, lower, weight, eps, state, ctx, heads, dim,
+                               vdim, out_dtype):
+        out = torch.empty((q_raw.shape[0], heads * vdim), dtype=torch.float32)
+        f = lower + (1 - lower) * torch.sigmoid(forget_raw + forget_bias)
+        q = torch.nn.functional.silu(q_raw)
+        for segment in ctx.segments:
+            S = state[segment.slot]
+            for row in range(segment.row_start, segment.row_start + segment.length):
+                S = f[row].view(heads, dim, 1) * S + (1 - f[row]).view(heads, dim, 1) * v[row].view(heads, 1, vdim)
+                o = torch.einsum("hi,hij->hj", q[row].view(heads, dim), S)
+                out[row] = (o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * weight).reshape(-1)
+            state[segment.slot] = S
+        return out.to(out_dtype)
+
+    def add_residual(self, residual, a, b=None):
+        residual += a if b is None else a + b
+        return residual
+
+    def gated_activation(self, gate_up, block, activation):
+        inner = gate_up.shape[1] // 2
+        blocks = gate_up.float().view(gate_up.shape[0], inner // block, 2, block)
+        gate, up = blocks[:, :, 0].reshape(-1, inner), blocks[:, :, 1].reshape(-1, inner)
+        act = torch.nn.functional.silu(gate) if activation == "silu" else torch.nn.functional.gelu(gate, approximate="tanh")
+        return (act * up).to(gate_up.dtype)
+
+    def linear_gated(self, x, weight, block, activation):
+        return self.gated_activation(self.linear(x, weight), block, activation)
+
+    def tanh_(self, x):
+        return x.copy_(torch.tanh(x.float()).to(x.dtype))
+
+    def qk_norm_kv_write(self, qkv, q_weight, k_weight, eps, slots, k_pool, v_pool, heads, kv_heads, dim, vdim,
+                         write_kv=True):
+        rows, page_size = qkv.shape[0], k_pool.shape[2]
+        nq, nk = 2 * heads * dim, 2 * kv_heads * dim
+
+        def normed(t, weight):
+            t = t.reshape(rows, -1, dim)
+            return (t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * weight).reshape(rows, -1)
+
+        q = normed(qkv[:, :nq], q_weight)
+        k = normed(qkv[:, nq:nq + nk], k_weight).view(rows, kv_heads, 2 * dim)
+        v = qkv[:, nq + nk:].reshape(rows, kv_heads, vdim)
+        if write_kv:
+            for t in range(rows):
+                page, offset = divmod(int(slots[t]), page_size)
+                k_pool[page, :, offset, :] = k[t].to(k_pool.dtype)
+                v_pool[page, :, offset, :] = v[t].to(v_pool.dtype)
+        return q.to(k_pool.dtype)
+
+    def differential_attention(self, q, k_pool, v_pool, batch, heads, kv_heads, dim, vdim, scale, window, keep_first,
+                               lam, eps, out_scale):
+        page_size, group = k_pool.shape[2], heads // kv_heads
+        out = torch.empty((q.shape[0], heads * vdim), dtype=q.dtype)
+        q4 = q.float().view(-1, heads, 2, dim)
+        for seg in range(batch.num_segments):
+            start, length, pos0 = int(batch.seg_q_start[seg]), int(batch.seg_q_len[seg]), int(batch.seg_pos0[seg])
+            table = batch.block_table[int(batch.seg_slot[seg])]
+            for r in range(length):
+                p = pos0 + r
+                keys = torch.tensor([j for j in range(p + 1) if not window or p - j < window or j < keep_first])
+                pages = table[(keys // page_size).long()].long()
+                assert (pages >= 0).all(), "attention reads a page the request does not hold"
+                offsets = (keys % page_size).long()
+                k = k_pool[pages, :, offsets, :].float().view(len(keys), kv_heads, 2, dim).repeat_interleave(group, dim=1)
+                v = v_pool[pages, :, offsets, :].float().repeat_interleave(group, dim=1)
+                weights = torch.softmax(torch.einsum("hmd,khmd->hmk", q4[start + r], k) * scale, dim=-1)
+                maps = torch.einsum("hmk,khd->hmd", weights, v)
+                o = maps[:, 0] - lam * maps[:, 1]
+                o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * out_scale
+                out[start + r] = o.reshape(-1).to(q.dtype)
+        return out
