@@ -42,13 +42,15 @@ def gated_feed_forward(h, gate, up, down):
 
 
 def visible(i: int, j: int, window: int, keep_first: int) -> bool:
-    return j <= i and (i - j < window or j < keep_first)
+    """window 0 stands for "no window": every earlier key is seen."""
+    return j <= i and (not window or i - j < window or j < keep_first)
 
 
 def differential_attention(h, t, prefix, mixer, eps):
     """Two softmax maps per head over shared values, combined as a1 - lambda * a2."""
     heads, groups, dim, vdim = mixer["heads"], mixer["kv_heads"], mixer["dim"], mixer["vdim"]
-    window, keep_first = mixer["mask"]["size"], mixer["mask"]["keep_first"]
+    mask = mixer.get("mask") or {"size": 0, "keep_first": 0}
+    window, keep_first = mask["size"], mask.get("keep_first", 0)
     scale, diff = mixer["scale"], mixer["diff"]
     length = h.shape[0]
     q = (h @ t[prefix + "q"].T).reshape(length, heads, 2, dim)
@@ -65,9 +67,9 @@ def differential_attention(h, t, prefix, mixer, eps):
             group = head // (heads // groups)
             maps = []
             for m in range(2):
-                scores = torch.stack([(q[i, head, m] * k[j, group, m]).sum() * scale for j in keys])
+                scores = (k[keys, group, m] @ q[i, head, m]) * scale
                 weights = torch.softmax(scores, dim=0)
-                maps.append((weights[:, None] * v[keys, group]).sum(dim=0))
+                maps.append(weights @ v[keys, group])
             o = maps[0] - lam * maps[1]
             out[i, head] = unit_rms(o, eps) * (1.0 - diff)
     return out.reshape(length, heads * vdim) @ t[prefix + "o"].T
