@@ -230,6 +230,42 @@ attention_diff_kernel(const T* q, const T* k_pool, const T* v_pool, T* __restric
   }
 }
 
+// q . k over n entries, q in shared memory as floats, k a row of the pool: 16-byte loads where the
+// row's start and length allow them.
+__device__ __forceinline__ float dot_row(const float* q, const float* k, int n) {
+  float s = 0.f;
+  if ((n & 3) == 0 && (reinterpret_cast<uintptr_t>(k) & 15) == 0) {
+    const float4* k4 = reinterpret_cast<const float4*>(k);
+    for (int d = 0; d < n / 4; ++d) {
+      const float4 kk = k4[d];
+      s = fmaf(q[4 * d], kk.x, s); s = fmaf(q[4 * d + 1], kk.y, s);
+      s = fmaf(q[4 * d + 2], kk.z, s); s = fmaf(q[4 * d + 3], kk.w, s);
+    }
+    return s;
+  }
+  for (int d = 0; d < n; ++d) s = fmaf(q[d], k[d], s);
+  return s;
+}
+__device__ __forceinline__ float dot_row(const float* q, const bf16* k, int n) {
+  float s = 0.f;
+  if ((n & 7) == 0 && (reinterpret_cast<uintptr_t>(k) & 15) == 0) {
+    const uint4* k8 = reinterpret_cast<const uint4*>(k);
+    for (int d = 0; d < n / 8; ++d) {
+      const uint4 kk = k8[d];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&kk);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        s = fmaf(q[8 * d + 2 * e], f.x, s);
+        s = fmaf(q[8 * d + 2 * e + 1], f.y, s);
+      }
+    }
+    return s;
+  }
+  for (int d = 0; d < n; ++d) s = fmaf(q[d], __bfloat162float(k[d]), s);
+  return s;
+}
+
 // ------------------------------------------------------------------ decoded rows
 // One CTA of DECODE_WARPS warps per (segment of one row, head).  Warp w takes the visible key tiles
 // number w, w + DECODE_WARPS, ..; each lane scores one key of a tile.  The warps' running states
@@ -242,9 +278,10 @@ attention_diff_decode_kernel(const T* q, const T* k_pool, const T* v_pool, T* __
                              const int* __restrict__ decode_seg, DiffArgs p) {
   pdl_trigger();
   pdl_wait();
-  extern __shared__ float shared[];
+  extern __shared__ __align__(16) float shared[];
   const int QK = 2 * p.dim, D = p.dim, V = p.vdim;
-  float* q_row = shared;                                        // [QK]
+  long long* places = reinterpret_cast<long long*>(shared);     // [warps][32]
+  float* q_row = shared + 2 * DECODE_WARPS * KEYS_PER_TILE;     // [QK]
   float* probs = q_row + QK;                                    // [warps][2][32]
   float* merged = probs + DECODE_WARPS * 2 * KEYS_PER_TILE;     // [warps][2][V + 2]
   const int seg = decode_seg != nullptr ? decode_seg[blockIdx.x] : blockIdx.x, head = blockIdx.y;
@@ -268,31 +305,29 @@ attention_diff_decode_kernel(const T* q, const T* k_pool, const T* v_pool, T* __
   const int kept = p.window > 0 ? min(p.keep_first, lowest) : 0;      // kept positions below the window
   const int total = kept + (pos - lowest + 1);
   float* pw = probs + warp * 2 * KEYS_PER_TILE;
+  long long* place = places + warp * KEYS_PER_TILE;       // row of each of the tile's keys in the pools, -1: none
   for (int t0 = warp * KEYS_PER_TILE; t0 < total; t0 += DECODE_WARPS * KEYS_PER_TILE) {
     const int entry = t0 + lane;
-    const bool valid = entry < total;
-    const int key = entry < kept ? entry : lowest + (entry - kept);
-    const T* kr = nullptr;
-    int page = -1;
-    if (valid) {
-      page = table[key / p.page_size];
-      if (page >= 0) kr = k_pool + (((size_t)page * p.kv_heads + kv_head) * p.page_size + key % p.page_size) * QK;
+    long long at = -1;
+    if (entry < total) {
+      const int key = entry < kept ? entry : lowest + (entry - kept);
+      const int page = table[key / p.page_size];
+      if (page >= 0) at = ((long long)page * p.kv_heads + kv_head) * p.page_size + key % p.page_size;
     }
+    place[lane] = at;
     float alpha[2];
 #pragma unroll
     for (int a = 0; a < 2; ++a) {
       float s = -INFINITY;
-      if (kr != nullptr) {
-        s = 0.f;
-        for (int d = 0; d < D; ++d) s = fmaf(q_row[a * D + d], to_float(kr[a * D + d]), s);
-        s *= p.scale;
+      if (at >= 0) {
+        s = dot_row(q_row + a * D, k_pool + at * QK + a * D, D) * p.scale;
       }
       const float m_new = fmaxf(m[a], warp_max(s));
       float prob = 0.f;
       alpha[a] = 1.f;
       if (m_new != -INFINITY) {
         alpha[a] = expf(m[a] - m_new);
-        prob = kr != nullptr ? expf(s - m_new) : 0.f;
+        prob = at >= 0 ? expf(s - m_new) : 0.f;
         l[a] = l[a] * alpha[a] + warp_sum(prob);
         m[a] = m_new;
       }
@@ -306,11 +341,9 @@ attention_diff_decode_kernel(const T* q, const T* k_pool, const T* v_pool, T* __
       if (d < V) {
         float a1 = acc[0][c] * alpha[0], a2 = acc[1][c] * alpha[1];
         for (int j = 0; j < count; ++j) {
-          const int e = t0 + j;
-          const int kj = e < kept ? e : lowest + (e - kept);
-          const int pg = table[kj / p.page_size];
-          if (pg < 0) continue;
-          const float vv = to_float(v_pool[(((size_t)pg * p.kv_heads + kv_head) * p.page_size + kj % p.page_size) * V + d]);
+          const long long row_at = place[j];
+          if (row_at < 0) continue;
+          const float vv = to_float(v_pool[row_at * V + d]);
           a1 = fmaf(pw[j], vv, a1);
           a2 = fmaf(pw[KEYS_PER_TILE + j], vv, a2);
         }
@@ -397,7 +430,8 @@ template <typename T>
 int attention_diff_decode_launch(const void* q, const void* k_pool, const void* v_pool, void* out,
                                  const int* decode_seg, int count, const DiffArgs& args, cudaStream_t stream) {
   const size_t shared = sizeof(float) * ((size_t)2 * args.dim + (size_t)DECODE_WARPS * 2 * KEYS_PER_TILE +
-                                         (size_t)DECODE_WARPS * 2 * (args.vdim + 2));
+                                         (size_t)DECODE_WARPS * 2 * (args.vdim + 2)) +
+                        sizeof(long long) * DECODE_WARPS * KEYS_PER_TILE;
   launch_kernel(attention_diff_decode_kernel<T>, dim3(count, args.heads), dim3(DECODE_WARPS * 32), shared, stream,
                 (const T*)q, (const T*)k_pool, (const T*)v_pool, (T*)out, decode_seg, args);
   return launch_status();

@@ -115,6 +115,14 @@ __device__ __forceinline__ float silu_times(float gate, float up) {
   return __fdividef(gate * up, 1.f + e);
 }
 
+// act(gate) * up for the gated feed-forwards: act 0 is silu, act 1 the tanh form of gelu, which is
+// z * sigmoid(2 sqrt(2/pi) (z + 0.044715 z^3)) and so costs the same one exponential and division.
+__device__ __forceinline__ float gate_times(int act, float gate, float up) {
+  const float z = act == 1 ? 1.5957691216057308f * fmaf(0.044715f * gate * gate, gate, gate) : gate;
+  const float e = __expf(fminf(-z, 80.f));
+  return __fdividef(gate * up, 1.f + e);
+}
+
 // One rotate-half pair: (x1, x2) turned by the angle whose sine and cosine are given.  Written with
 // explicit roundings so that every kernel that rotates gets the same bits.
 __device__ __forceinline__ void rotate_pair(float x1, float x2, float sine, float cosine, float* y1, float* y2) {

@@ -239,7 +239,8 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, const bf16* __rest
         const int half = N >> 1;
         if (column < half) {
           const float gate = acc[0][n][e] * scale, up = acc[GROUPS - 1][n][e] * scale;
-          out_bf16[(size_t)token * half + column] = __float2bfloat16_rn(silu_times(gate, up));
+          // gated products always leave bfloat16: their out_f32 argument carries the gate's activation
+          out_bf16[(size_t)token * half + column] = __float2bfloat16_rn(gate_times(out_f32, gate, up));
         }
       } else {
         if (ROWS8 && e >= 2) continue;                     // the MMA's upper rows hold nothing
@@ -297,10 +298,10 @@ static int skinny_launch(const void* x, const void* w, const void* bias, void* o
       if constexpr (WARPS == 4 && TOKENS8 == 1) {
         // rows of at most 7 k blocks per warp (896 wide): a batch of 7 leaves registers for a third CTA per SM
         if ((K + 31) / 32 <= 7 * WARPS)
-          return skinny_launch_one<WARPS, 2, TOKENS8, true, 7>(x, w, bias, out, residual, M, N, K, out_f32, rms_eps,
+          return skinny_launch_one<WARPS, 2, TOKENS8, true, 7>(x, w, bias, out, residual, M, N, K, swiglu == 2, rms_eps,
                                                                (N / 2 + 15) / 16, stream, rounds_out);
       }
-      return skinny_launch_one<WARPS, 2, TOKENS8, true>(x, w, bias, out, residual, M, N, K, out_f32, rms_eps,
+      return skinny_launch_one<WARPS, 2, TOKENS8, true>(x, w, bias, out, residual, M, N, K, swiglu == 2, rms_eps,
                                                         (N / 2 + 15) / 16, stream, rounds_out);
     }
   }
@@ -349,7 +350,8 @@ static int skinny_dispatch(const void* x, const void* w, const void* bias, void*
 
 
 // x [M,K], w [N,K], bias [N] or null (bfloat16); out [M,N] bfloat16 or float32 (out_f32).
-// swiglu != 0: w interleaves blocks of 64 gate rows with the 64 up rows of the same outputs
+// swiglu != 0: w interleaves blocks of 64 gate rows with the 64 up rows of the same outputs; the
+// result is silu(gate) * up (swiglu == 1) or gelu_tanh(gate) * up (swiglu == 2)
 // (N % 128 == 0, no bias); out is silu(gate) * up, [M, N/2] bfloat16.  M <= 64, K % 8 == 0.
 // rms_eps >= 0: the product acts on the RMS-normalised rows of x.  residual: [M,N] bfloat16 added
 // to the result (it may be `out`), or null; not with swiglu.

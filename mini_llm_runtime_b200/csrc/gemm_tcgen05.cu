@@ -129,6 +129,7 @@ struct GemmParams {
   const bf16* bias;
   void* out;
   int out_f32;
+  int gate_act;             // gated products: 0 silu(gate) * up, 1 gelu_tanh(gate) * up
   float* scratch;           // [tiles][splits][BN][128] partial tiles (splits > 1)
   int* counters;            // one per output tile, zero between launches
   int* error_word;
@@ -258,8 +259,8 @@ __device__ __forceinline__ void reduce_swapped_swiglu(const float* partials, int
     for (int j = 0; j < CB; ++j) {
       const int col = c + 8 * j, m = b_row0 + col;
       if (col >= BN || m >= p.M) continue;
-      const float v[4] = {silu_times(gate[j].x, up[j].x), silu_times(gate[j].y, up[j].y),
-                          silu_times(gate[j].z, up[j].z), silu_times(gate[j].w, up[j].w)};
+      const float v[4] = {gate_times(p.gate_act, gate[j].x, up[j].x), gate_times(p.gate_act, gate[j].y, up[j].y),
+                          gate_times(p.gate_act, gate[j].z, up[j].z), gate_times(p.gate_act, gate[j].w, up[j].w)};
       bf16* dst = (bf16*)p.out + (size_t)m * half + n0;
       if (wide) {
         __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
@@ -485,8 +486,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int c = 0; c < 16; c += 2) {
               __nv_bfloat162 pair = __floats2bfloat162_rn(
-                  silu_times(__uint_as_float(g[q + c]), __uint_as_float(u[q + c])),
-                  silu_times(__uint_as_float(g[q + c + 1]), __uint_as_float(u[q + c + 1])));
+                  gate_times(p.gate_act, __uint_as_float(g[q + c]), __uint_as_float(u[q + c])),
+                  gate_times(p.gate_act, __uint_as_float(g[q + c + 1]), __uint_as_float(u[q + c + 1])));
               packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
             }
             if ((half & 7) == 0 && n0 + 16 <= half) {
@@ -777,7 +778,8 @@ MLR_EXPORT long long mlr_gemm_tcgen05_plan(int M, int N, int K, int swiglu, int*
 }
 
 // x [M,K], w [N,K], bias [N] or null, all bfloat16; out [M,N] bfloat16 (out_f32 = 0) or float32.
-// swiglu != 0: w holds blocks of 64 gate rows followed by the 64 up rows of the same outputs
+// swiglu != 0: w holds blocks of 64 gate rows followed by the 64 up rows of the same outputs and the
+// result is act(gate) * up, act being silu (swiglu == 1) or the tanh form of gelu (swiglu == 2)
 // (N % 128 == 0, no bias) and out is silu(gate) * up, [M, N/2] bfloat16.
 // scratch: at least mlr_gemm_tcgen05_plan(...) bytes; counters: one zeroed int per tile;
 // error_word: host-visible int that receives a non-zero code if a wait inside the kernel runs out.
@@ -797,6 +799,7 @@ MLR_EXPORT int mlr_gemm_tcgen05(const void* x, const void* w, const void* bias, 
   p.bias = (const bf16*)bias;
   p.out = out;
   p.out_f32 = out_f32;
+  p.gate_act = swiglu == 2 ? 1 : 0;
   p.scratch = (float*)scratch;
   p.counters = counters;
   p.error_word = error_word;

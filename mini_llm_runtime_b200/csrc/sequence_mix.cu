@@ -113,11 +113,15 @@ save_last_rows_kernel(const float* a, float* state, const int* __restrict__ seg_
 //                    a = lower + (1 - lower) * sigmoid(raw + bias), b = 1 - a, r = silu(raw r);
 //                    out = o / rms(o) * weight[j]
 //
+// The bonus term is taken out of the sum over key channels: o_t[j] = sum_i r[i] S[i][j] +
+// v[j] * sum_i r[i] c[i] b[i], one dot product per token instead of one more product per state entry.
+//
 // One CTA per (head, segment).  Thread (j, s) keeps rows s*KD .. s*KD+KD-1 of column j of S in
 // registers.  Tokens are taken in chunks of REC_CHUNK: the chunk's inputs are transformed (the
 // exponentials) by all threads at once into shared memory, the recurrence then runs token by token on
-// registers with no barrier, the partial sums of the key slices are added in slice order, and the
-// chunk's outputs are normalised one warp per token.
+// registers with no barrier (inputs read four key channels per load, two running sums), the partial
+// sums of the key slices are added in slice order, and the chunk's outputs are normalised one warp
+// per token.
 constexpr int REC_CHUNK = 16;
 
 struct RecurrenceArgs {
@@ -135,20 +139,21 @@ __global__ void __launch_bounds__(512)
 gated_recurrence_kernel(RecurrenceArgs p, T* __restrict__ out) {
   pdl_trigger();
   pdl_wait();
-  extern __shared__ float shared[];
+  extern __shared__ __align__(16) float shared[];
   const int dim = p.dim, vdim = p.vdim;
   const int slices = blockDim.y, dim_pad = slices * KD;
   float* s_r = shared;                              // [CHUNK][dim_pad]
   float* s_a = s_r + REC_CHUNK * dim_pad;
   float* s_b = s_a + REC_CHUNK * dim_pad;
-  float* s_c = s_b + REC_CHUNK * dim_pad;           // [dim_pad] bonus (mode 0)
-  float* s_v = s_c + dim_pad;                       // [CHUNK][vdim]
+  float* s_bonus = s_b + REC_CHUNK * dim_pad;       // [CHUNK] sum_i r c b (mode 0)
+  float* s_v = s_bonus + REC_CHUNK;                 // [CHUNK][vdim]
   float* s_o = s_v + REC_CHUNK * vdim;              // [slices][CHUNK][vdim]
 
   const int head = blockIdx.x, seg = blockIdx.y;
   const int length = p.seg_q_len[seg], first = p.seg_q_start[seg];
   const int j = threadIdx.x, slice = threadIdx.y;
   const int tid = threadIdx.y * blockDim.x + threadIdx.x, threads = blockDim.x * blockDim.y;
+  const int warp = tid >> 5, lane = tid & 31, warps = threads >> 5;
   const bool owner = j < vdim;
   float* state = p.state + ((size_t)p.seg_slot[seg] * p.heads + head) * dim * vdim;
 
@@ -158,8 +163,6 @@ gated_recurrence_kernel(RecurrenceArgs p, T* __restrict__ out) {
     const int row = slice * KD + i;
     S[i] = (owner && row < dim) ? state[(size_t)row * vdim + j] : 0.f;
   }
-  for (int i = tid; i < dim_pad; i += threads)
-    s_c[i] = (MODE == 0 && i < dim) ? p.aux[head * dim + i] : 0.f;
 
   for (int t0 = 0; t0 < length; t0 += REC_CHUNK) {
     const int count = min(REC_CHUNK, length - t0);
@@ -191,36 +194,50 @@ gated_recurrence_kernel(RecurrenceArgs p, T* __restrict__ out) {
       s_v[idx] = p.v[(size_t)(first + t0 + t) * p.v_stride + head * vdim + c];
     }
     __syncthreads();
+    if (MODE == 0) {
+      for (int t = warp; t < count; t += warps) {
+        float dot = 0.f;
+        for (int i = lane; i < dim; i += 32)
+          dot = fmaf(s_r[t * dim_pad + i] * p.aux[head * dim + i], s_b[t * dim_pad + i], dot);
+        dot = warp_sum(dot);
+        if (lane == 0) s_bonus[t] = dot;
+      }
+    }
     if (owner) {
       for (int t = 0; t < count; ++t) {
         const float v = s_v[t * vdim + j];
-        const float* rr = s_r + t * dim_pad + slice * KD;
-        const float* aa = s_a + t * dim_pad + slice * KD;
-        const float* bb = s_b + t * dim_pad + slice * KD;
-        const float* cc = s_c + slice * KD;
-        float o = 0.f;
+        const float4* rr = reinterpret_cast<const float4*>(s_r + t * dim_pad + slice * KD);
+        const float4* aa = reinterpret_cast<const float4*>(s_a + t * dim_pad + slice * KD);
+        const float4* bb = reinterpret_cast<const float4*>(s_b + t * dim_pad + slice * KD);
+        float o0 = 0.f, o1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < KD; ++i) {
-          const float kv = bb[i] * v;
+        for (int i4 = 0; i4 < KD / 4; ++i4) {
+          const float4 r = rr[i4], a = aa[i4], b = bb[i4];
+          float* s = S + 4 * i4;
           if (MODE == 0) {
-            o = fmaf(rr[i], fmaf(cc[i], kv, S[i]), o);
-            S[i] = fmaf(aa[i], S[i], kv);
+            o0 = fmaf(r.x, s[0], o0); o1 = fmaf(r.y, s[1], o1);
+            o0 = fmaf(r.z, s[2], o0); o1 = fmaf(r.w, s[3], o1);
+            s[0] = fmaf(a.x, s[0], b.x * v); s[1] = fmaf(a.y, s[1], b.y * v);
+            s[2] = fmaf(a.z, s[2], b.z * v); s[3] = fmaf(a.w, s[3], b.w * v);
           } else {
-            S[i] = fmaf(aa[i], S[i], kv);
-            o = fmaf(rr[i], S[i], o);
+            s[0] = fmaf(a.x, s[0], b.x * v); s[1] = fmaf(a.y, s[1], b.y * v);
+            s[2] = fmaf(a.z, s[2], b.z * v); s[3] = fmaf(a.w, s[3], b.w * v);
+            o0 = fmaf(r.x, s[0], o0); o1 = fmaf(r.y, s[1], o1);
+            o0 = fmaf(r.z, s[2], o0); o1 = fmaf(r.w, s[3], o1);
           }
         }
-        s_o[(slice * REC_CHUNK + t) * vdim + j] = o;
+        s_o[(slice * REC_CHUNK + t) * vdim + j] = o0 + o1;
       }
     }
     __syncthreads();
     // normalise and write: one warp per token, lanes over the value channels
-    const int warp = tid >> 5, lane = tid & 31, warps = threads >> 5;
     for (int t = warp; t < count; t += warps) {
       float sq = 0.f;
+      const float bonus = MODE == 0 ? s_bonus[t] : 0.f;
       for (int c = lane; c < vdim; c += 32) {
         float o = 0.f;
         for (int s = 0; s < slices; ++s) o += s_o[(s * REC_CHUNK + t) * vdim + c];
+        if (MODE == 0) o = fmaf(s_v[t * vdim + c], bonus, o);
         s_o[t * vdim + c] = o;      // slice 0's place now holds the sum (same lane reads it below)
         sq = fmaf(o, o, sq);
       }
@@ -290,14 +307,16 @@ __global__ void tanh_kernel(T* x, long long count) {
 template <typename T, int MODE>
 int launch_recurrence(const RecurrenceArgs& args, void* out, int segments, cudaStream_t stream) {
   const int vp = (args.vdim + 31) / 32 * 32;
-  int kd = 32;      // key channels per thread: 32 unless that would need more than 512 threads
-  if (vp * ((args.dim + 31) / 32) > 512) kd = 64;
+  // key channels per thread: the fewest of 16, 32, 64 with which a CTA stays within 512 threads
+  int kd = 16;
+  while (kd < 64 && vp * ((args.dim + kd - 1) / kd) > 512) kd *= 2;
   const int slices = (args.dim + kd - 1) / kd;
   if (vp * slices > 512) return MLR_TOO_LARGE;
   const int dim_pad = slices * kd;
-  const size_t shared = sizeof(float) * ((size_t)3 * REC_CHUNK * dim_pad + dim_pad + (size_t)REC_CHUNK * args.vdim +
+  const size_t shared = sizeof(float) * ((size_t)3 * REC_CHUNK * dim_pad + REC_CHUNK + (size_t)REC_CHUNK * args.vdim +
                                          (size_t)slices * REC_CHUNK * args.vdim);
-  auto kernel = kd == 32 ? gated_recurrence_kernel<T, MODE, 32> : gated_recurrence_kernel<T, MODE, 64>;
+  auto kernel = kd == 16 ? gated_recurrence_kernel<T, MODE, 16>
+                : kd == 32 ? gated_recurrence_kernel<T, MODE, 32> : gated_recurrence_kernel<T, MODE, 64>;
   if (shared > 200 * 1024) return MLR_TOO_LARGE;
   if (shared > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);

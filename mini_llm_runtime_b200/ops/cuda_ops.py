@@ -316,27 +316,29 @@ class CudaOps:
     SWIGLU_BLOCK = 64   # rows of gate, then rows of up, per 128-row weight tile of the fused kernel
 
     def linear_swiglu(self, x: torch.Tensor, weight: torch.Tensor, block: int,
-                      rms_eps: float | None = None) -> torch.Tensor:
-        """silu(x Wg^T) * (x Wu^T) where ``weight`` [2*inner, K] interleaves ``block`` gate rows
-        with the ``block`` up rows of the same outputs.  One tensor-core kernel when the shapes
-        allow (block 64), else the product followed by the activation kernel.  ``rms_eps`` as in
-        ``linear``."""
+                      rms_eps: float | None = None, activation: str = "silu") -> torch.Tensor:
+        """act(x Wg^T) * (x Wu^T) where ``weight`` [2*inner, K] interleaves ``block`` gate rows
+        with the ``block`` up rows of the same outputs; act is silu or, with ``activation=
+        "gelu_tanh"``, the tanh form of gelu.  One tensor-core kernel when the shapes allow (block
+        64), else the product followed by the activation kernel.  ``rms_eps`` as in ``linear``."""
         _need(x, "x", dims=2)
         _need(weight, "weight", x.dtype, 2)
         if x.shape[1] != weight.shape[1] or weight.shape[0] % (2 * block):
             raise KernelError("linear_swiglu: shapes do not fit the interleaved gate/up layout")
+        code = 1 + self.GATE_ACTIVATIONS[activation]        # the kernels' flag: 1 silu, 2 gelu_tanh
         if (self.use_tensor_cores and self.use_fused_swiglu and block == self.SWIGLU_BLOCK
                 and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.shape[0] > 0
                 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
             if self._skinny_fits(x, weight, swiglu=True):
-                return self._linear_skinny(x, weight, None, torch.bfloat16, swiglu=True, rms_eps=rms_eps)
+                return self._linear_skinny(x, weight, None, torch.bfloat16, swiglu=code, rms_eps=rms_eps)
             if rms_eps is not None:
                 x = self.rms_norm(x, None, rms_eps)
                 rms_eps = None
-            out = self._linear_tcgen05(x, weight, None, torch.bfloat16, swiglu=True)
+            out = self._linear_tcgen05(x, weight, None, torch.bfloat16, swiglu=code)
             if out is not None:
                 return out
-        return self.swiglu(self.linear(x, weight, rms_eps=rms_eps), block)
+        product = self.linear(x, weight, rms_eps=rms_eps)
+        return self.swiglu(product, block) if activation == "silu" else self.gated_activation(product, block, activation)
 
     def rope_kv_write(self, qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
                       slots: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, num_heads: int,
@@ -906,9 +908,7 @@ class CudaOps:
 
     def linear_gated(self, x: torch.Tensor, weight: torch.Tensor, block: int, activation: str) -> torch.Tensor:
         """act(x Wg^T) * (x Wu^T) for ``weight`` [2*inner, K] of interleaved gate/up blocks."""
-        if activation == "silu":
-            return self.linear_swiglu(x, weight, block)
-        return self.gated_activation(self.linear(x, weight), block, activation)
+        return self.linear_swiglu(x, weight, block, activation=activation)
 
     def tanh_(self, x: torch.Tensor) -> torch.Tensor:
         _need(x, "x")

@@ -229,3 +229,21 @@ def test_greedy_generation_through_the_scheduler():
         for _ in range(12):
             sequence.append(int(torch.argmax(engine_parts.plain(sequence)[-1])))
         assert got == sequence[len(prompt):]
+
+
+@pytest.mark.parametrize("rows", [1, 8, 40, 130, 700])
+@pytest.mark.parametrize("inner,width", [(256, 128), (1216, 896)])
+def test_gated_product_with_the_gelu_epilogue(rows, inner, width):
+    """gelu_tanh(x Wg^T) * (x Wu^T) from the products' own epilogues (few rows, many rows) against
+    the formula, on weights interleaved in blocks of 64."""
+    from mini_llm_runtime_b200 import ops
+
+    generator = torch.Generator().manual_seed(rows + inner)
+    x = torch.randn(rows, width, generator=generator).to(torch.bfloat16)
+    gate = (torch.randn(inner, width, generator=generator) / width ** 0.5 * 2).to(torch.bfloat16)
+    up = (torch.randn(inner, width, generator=generator) / width ** 0.5).to(torch.bfloat16)
+    stacked = torch.cat([gate.view(-1, 64, width), up.view(-1, 64, width)], dim=1).reshape(2 * inner, width)
+    got = ops.current().linear_gated(x.to(DEVICE), stacked.to(DEVICE).contiguous(), 64, "gelu_tanh")
+    want = plain.gelu_tanh(x.double() @ gate.double().T) * (x.double() @ up.double().T)
+    error = (got.double().cpu() - want).abs().max() / want.abs().max()
+    assert float(error) < 1e-2
