@@ -340,12 +340,14 @@ attention_diff_decode_kernel(const T* q, const T* k_pool, const T* v_pool, T* __
       const int d = lane + 32 * c;
       if (d < V) {
         float a1 = acc[0][c] * alpha[0], a2 = acc[1][c] * alpha[1];
-        for (int j = 0; j < count; ++j) {
-          const long long row_at = place[j];
-          if (row_at < 0) continue;
+        // a key without a page has probability 0: its load is pointed at row 0 and adds nothing, so
+        // that the loads of several keys can be in flight at once
+#pragma unroll 8
+        for (int j = 0; j < KEYS_PER_TILE; ++j) {
+          const long long row_at = j < count ? max(place[j], 0LL) : 0LL;
           const float vv = to_float(v_pool[row_at * V + d]);
-          a1 = fmaf(pw[j], vv, a1);
-          a2 = fmaf(pw[KEYS_PER_TILE + j], vv, a2);
+          a1 = fmaf(j < count ? pw[j] : 0.f, vv, a1);
+          a2 = fmaf(j < count ? pw[KEYS_PER_TILE + j] : 0.f, vv, a2);
         }
         acc[0][c] = a1;
         acc[1][c] = a2;

@@ -204,7 +204,8 @@ gated_recurrence_kernel(RecurrenceArgs p, T* __restrict__ out) {
       }
     }
     if (owner) {
-      for (int t = 0; t < count; ++t) {
+      // one token: the thread's KD state rows against the token's r, a, b (four channels per load)
+      auto one_token = [&](int t) {
         const float v = s_v[t * vdim + j];
         const float4* rr = reinterpret_cast<const float4*>(s_r + t * dim_pad + slice * KD);
         const float4* aa = reinterpret_cast<const float4*>(s_a + t * dim_pad + slice * KD);
@@ -227,6 +228,13 @@ gated_recurrence_kernel(RecurrenceArgs p, T* __restrict__ out) {
           }
         }
         s_o[(slice * REC_CHUNK + t) * vdim + j] = o0 + o1;
+      };
+      if (KD <= 32 && count == REC_CHUNK) {
+        // a full chunk: unrolled (not with 64 rows per thread: the registers run out), so that the next tokens' loads are issued under this token's arithmetic
+#pragma unroll
+        for (int t = 0; t < REC_CHUNK; ++t) one_token(t);
+      } else {
+        for (int t = 0; t < count; ++t) one_token(t);
       }
     }
     __syncthreads();
@@ -307,15 +315,16 @@ __global__ void tanh_kernel(T* x, long long count) {
 template <typename T, int MODE>
 int launch_recurrence(const RecurrenceArgs& args, void* out, int segments, cudaStream_t stream) {
   const int vp = (args.vdim + 31) / 32 * 32;
-  // key channels per thread: the fewest of 16, 32, 64 with which a CTA stays within 512 threads
-  int kd = 16;
+  // key channels per thread: the fewest of 8, 16, 32, 64 with which a CTA stays within 512 threads
+  // (more threads with shorter chains hide the latency of the shared-memory loads that feed them)
+  int kd = 8;
   while (kd < 64 && vp * ((args.dim + kd - 1) / kd) > 512) kd *= 2;
   const int slices = (args.dim + kd - 1) / kd;
   if (vp * slices > 512) return MLR_TOO_LARGE;
   const int dim_pad = slices * kd;
   const size_t shared = sizeof(float) * ((size_t)3 * REC_CHUNK * dim_pad + REC_CHUNK + (size_t)REC_CHUNK * args.vdim +
                                          (size_t)slices * REC_CHUNK * args.vdim);
-  auto kernel = kd == 16 ? gated_recurrence_kernel<T, MODE, 16>
+  auto kernel = kd == 8 ? gated_recurrence_kernel<T, MODE, 8> : kd == 16 ? gated_recurrence_kernel<T, MODE, 16>
                 : kd == 32 ? gated_recurrence_kernel<T, MODE, 32> : gated_recurrence_kernel<T, MODE, 64>;
   if (shared > 200 * 1024) return MLR_TOO_LARGE;
   if (shared > 48 * 1024) {

@@ -44,6 +44,7 @@ LIBRARIES: dict[str, tuple[str, ...]] = {
     "attention_tcgen05": (),
     "sequence_mix": (),
     "attention_diff": (),
+    "attention_diff_mma": (),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

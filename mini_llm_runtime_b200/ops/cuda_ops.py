@@ -971,6 +971,19 @@ class CudaOps:
                 _ptr(batch.seg_q_start), _ptr(batch.seg_pos0), _ptr(batch.block_table), _ptr(batch.seg_slot),
                 batch.block_table.shape[1], *tail), "differential attention (decode)")
             tiles -= batch.num_decode       # the one-row segments' tiles are the last of the list
+        if (tiles > 0 and self.use_mma_attention and q.dtype == torch.bfloat16 and batch.counts.get("wide", 0) > 0
+                and dim in (64, 128) and vdim in (64, 128) and q.data_ptr() % 16 == 0
+                and (self.use_diff_decode_kernel or batch.num_decode == 0)):
+            # prompt portions on the tensor cores: each map as an attention of its own, then the combination
+            maps = torch.empty((q.shape[0], 2 * heads * vdim), dtype=torch.float32, device=q.device)
+            _check(build.load_library("attention_diff_mma").mlr_attention_diff_mma(
+                _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(maps), _ptr(out), _ptr(batch.plan["wide_tile_seg"]),
+                _ptr(batch.plan["wide_tile_row0"]), _ptr(batch.seg_q_start), _ptr(batch.seg_q_len),
+                _ptr(batch.seg_pos0), _ptr(batch.block_table), _ptr(batch.seg_slot), batch.block_table.shape[1],
+                batch.counts["wide"], heads, kv_heads, dim, vdim, k_pool.shape[2], int(window or 0), int(keep_first),
+                ctypes.c_float(scale), ctypes.c_float(lam), ctypes.c_float(eps), ctypes.c_float(out_scale), _stream()),
+                "differential attention (tensor cores)")
+            return out
         if tiles > 0:
             _check(lib.mlr_attention_diff(
                 _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(batch.plan["tile_seg"]),
