@@ -270,9 +270,12 @@ __device__ __forceinline__ float dot_row(const float* q, const bf16* k, int n) {
 // One CTA of DECODE_WARPS warps per (segment of one row, head).  Warp w takes the visible key tiles
 // number w, w + DECODE_WARPS, ..; each lane scores one key of a tile.  The warps' running states
 // (max, sum, value sums of both maps) are merged by warp 0 in warp order.
-constexpr int DECODE_WARPS = 8;
+constexpr int DECODE_WARPS = 32;      // about one 32-key tile per warp at a window of a thousand keys
 
-template <typename T>
+// WIDE (bfloat16 values, vdim a multiple of 8): a lane fetches eight adjacent value channels of one
+// key with one 16-byte load, 32 / lanes-per-key keys per warp-wide load, and the lane groups' sums are
+// added by shuffles after the last tile.
+template <typename T, bool WIDE>
 __global__ void __launch_bounds__(DECODE_WARPS * 32)
 attention_diff_decode_kernel(const T* q, const T* k_pool, const T* v_pool, T* __restrict__ out,
                              const int* __restrict__ decode_seg, DiffArgs p) {
@@ -299,6 +302,14 @@ attention_diff_decode_kernel(const T* q, const T* k_pool, const T* v_pool, T* __
   for (int a = 0; a < 2; ++a)
 #pragma unroll
     for (int c = 0; c < MAX_VDIM / 32; ++c) acc[a][c] = 0.f;
+
+  // WIDE: lanes_per_key lanes cover a value row, eight channels each; `sub` is the lane's key within a load
+  int lanes_per_key = 1;
+  while (lanes_per_key * 8 < V) lanes_per_key *= 2;
+  const int keys_per_load = 32 / lanes_per_key, sub = lane / lanes_per_key, d0 = (lane % lanes_per_key) * 8;
+  float wide[2][8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) wide[0][e] = wide[1][e] = 0.f;
 
   // the visible keys: [0, kept) and [lowest, pos]; as one list of tiles of 32 consecutive list entries
   const int lowest = p.window > 0 ? max(0, pos - p.window + 1) : 0;
@@ -335,27 +346,60 @@ attention_diff_decode_kernel(const T* q, const T* k_pool, const T* v_pool, T* __
     }
     __syncwarp();
     const int count = min(KEYS_PER_TILE, total - t0);
+    if (WIDE) {
 #pragma unroll
-    for (int c = 0; c < MAX_VDIM / 32; ++c) {
-      const int d = lane + 32 * c;
-      if (d < V) {
-        float a1 = acc[0][c] * alpha[0], a2 = acc[1][c] * alpha[1];
-        // a key without a page has probability 0: its load is pointed at row 0 and adds nothing, so
-        // that the loads of several keys can be in flight at once
-#pragma unroll 8
-        for (int j = 0; j < KEYS_PER_TILE; ++j) {
-          const long long row_at = j < count ? max(place[j], 0LL) : 0LL;
-          const float vv = to_float(v_pool[row_at * V + d]);
-          a1 = fmaf(j < count ? pw[j] : 0.f, vv, a1);
-          a2 = fmaf(j < count ? pw[KEYS_PER_TILE + j] : 0.f, vv, a2);
+      for (int e = 0; e < 8; ++e) {
+        wide[0][e] *= alpha[0];
+        wide[1][e] *= alpha[1];
+      }
+      // a key without a page has probability 0: its load is pointed at row 0 and adds nothing, so
+      // that the loads of a whole tile can be in flight at once
+#pragma unroll 4
+      for (int j0 = 0; j0 < KEYS_PER_TILE; j0 += keys_per_load) {
+        const int j = j0 + sub;
+        const bool live = j < count && d0 < V;
+        const long long row_at = live ? max(place[j], 0LL) : 0LL;
+        const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(v_pool) + row_at * V + (d0 < V ? d0 : 0));
+        const float p1 = live ? pw[j] : 0.f, p2 = live ? pw[KEYS_PER_TILE + j] : 0.f;
+        const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(pairs[e]);
+          wide[0][2 * e] = fmaf(p1, f.x, wide[0][2 * e]);
+          wide[0][2 * e + 1] = fmaf(p1, f.y, wide[0][2 * e + 1]);
+          wide[1][2 * e] = fmaf(p2, f.x, wide[1][2 * e]);
+          wide[1][2 * e + 1] = fmaf(p2, f.y, wide[1][2 * e + 1]);
         }
-        acc[0][c] = a1;
-        acc[1][c] = a2;
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < MAX_VDIM / 32; ++c) {
+        const int d = lane + 32 * c;
+        if (d < V) {
+          float a1 = acc[0][c] * alpha[0], a2 = acc[1][c] * alpha[1];
+#pragma unroll 8
+          for (int j = 0; j < KEYS_PER_TILE; ++j) {
+            const long long row_at = j < count ? max(place[j], 0LL) : 0LL;
+            const float vv = to_float(v_pool[row_at * V + d]);
+            a1 = fmaf(j < count ? pw[j] : 0.f, vv, a1);
+            a2 = fmaf(j < count ? pw[KEYS_PER_TILE + j] : 0.f, vv, a2);
+          }
+          acc[0][c] = a1;
+          acc[1][c] = a2;
+        }
       }
     }
     __syncwarp();
   }
   // hand the warp's state to warp 0
+  if (WIDE) {
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        for (int offset = lanes_per_key; offset < 32; offset <<= 1)
+          wide[a][e] += __shfl_xor_sync(0xffffffffu, wide[a][e], offset);
+  }
 #pragma unroll
   for (int a = 0; a < 2; ++a) {
     float* mine = merged + (size_t)(warp * 2 + a) * (V + 2);
@@ -363,10 +407,17 @@ attention_diff_decode_kernel(const T* q, const T* k_pool, const T* v_pool, T* __
       mine[V] = m[a];
       mine[V + 1] = l[a];
     }
+    if (WIDE) {
+      if (sub == 0 && d0 < V) {
 #pragma unroll
-    for (int c = 0; c < MAX_VDIM / 32; ++c) {
-      const int d = lane + 32 * c;
-      if (d < V) mine[d] = acc[a][c];
+        for (int e = 0; e < 8; ++e) mine[d0 + e] = wide[a][e];
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < MAX_VDIM / 32; ++c) {
+        const int d = lane + 32 * c;
+        if (d < V) mine[d] = acc[a][c];
+      }
     }
   }
   __syncthreads();
@@ -434,7 +485,13 @@ int attention_diff_decode_launch(const void* q, const void* k_pool, const void* 
   const size_t shared = sizeof(float) * ((size_t)2 * args.dim + (size_t)DECODE_WARPS * 2 * KEYS_PER_TILE +
                                          (size_t)DECODE_WARPS * 2 * (args.vdim + 2)) +
                         sizeof(long long) * DECODE_WARPS * KEYS_PER_TILE;
-  launch_kernel(attention_diff_decode_kernel<T>, dim3(count, args.heads), dim3(DECODE_WARPS * 32), shared, stream,
+  const bool wide = sizeof(T) == 2 && args.vdim % 8 == 0 && (reinterpret_cast<uintptr_t>(v_pool) & 15) == 0;
+  auto kernel = wide ? attention_diff_decode_kernel<T, true> : attention_diff_decode_kernel<T, false>;
+  if (shared > 48 * 1024) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    if (err != cudaSuccess) return (int)err;
+  }
+  launch_kernel(kernel, dim3(count, args.heads), dim3(DECODE_WARPS * 32), shared, stream,
                 (const T*)q, (const T*)k_pool, (const T*)v_pool, (T*)out, decode_seg, args);
   return launch_status();
 }

@@ -122,7 +122,7 @@ save_last_rows_kernel(const float* a, float* state, const int* __restrict__ seg_
 // registers with no barrier (inputs read four key channels per load, two running sums), the partial
 // sums of the key slices are added in slice order, and the chunk's outputs are normalised one warp
 // per token.
-constexpr int REC_CHUNK = 16;
+constexpr int REC_CHUNK = 32;
 
 struct RecurrenceArgs {
   const float *r, *b, *v, *raw, *gate;           // row-major views, one row per token
@@ -132,6 +132,8 @@ struct RecurrenceArgs {
   float* state;                                  // [slots, heads, dim, vdim]
   const int *seg_q_start, *seg_q_len, *seg_slot;
   int heads, dim, vdim, weight_per_head;
+  int columns;        // value channels per CTA: vdim, or a part of it (blockIdx.z picks the part)
+  float* raw_out;     // with parts: the un-normalised o [rows, heads*vdim]; recurrence_finish_kernel ends the job
 };
 
 template <typename T, int MODE, int KD>
@@ -140,7 +142,7 @@ gated_recurrence_kernel(RecurrenceArgs p, T* __restrict__ out) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ __align__(16) float shared[];
-  const int dim = p.dim, vdim = p.vdim;
+  const int dim = p.dim, vdim = p.columns, full = p.vdim, column0 = blockIdx.z * p.columns;
   const int slices = blockDim.y, dim_pad = slices * KD;
   float* s_r = shared;                              // [CHUNK][dim_pad]
   float* s_a = s_r + REC_CHUNK * dim_pad;
@@ -155,13 +157,13 @@ gated_recurrence_kernel(RecurrenceArgs p, T* __restrict__ out) {
   const int tid = threadIdx.y * blockDim.x + threadIdx.x, threads = blockDim.x * blockDim.y;
   const int warp = tid >> 5, lane = tid & 31, warps = threads >> 5;
   const bool owner = j < vdim;
-  float* state = p.state + ((size_t)p.seg_slot[seg] * p.heads + head) * dim * vdim;
+  float* state = p.state + ((size_t)p.seg_slot[seg] * p.heads + head) * dim * full + column0;
 
   float S[KD];
 #pragma unroll
   for (int i = 0; i < KD; ++i) {
     const int row = slice * KD + i;
-    S[i] = (owner && row < dim) ? state[(size_t)row * vdim + j] : 0.f;
+    S[i] = (owner && row < dim) ? state[(size_t)row * full + j] : 0.f;
   }
 
   for (int t0 = 0; t0 < length; t0 += REC_CHUNK) {
@@ -191,7 +193,7 @@ gated_recurrence_kernel(RecurrenceArgs p, T* __restrict__ out) {
     }
     for (int idx = tid; idx < count * vdim; idx += threads) {
       const int t = idx / vdim, c = idx - t * vdim;
-      s_v[idx] = p.v[(size_t)(first + t0 + t) * p.v_stride + head * vdim + c];
+      s_v[idx] = p.v[(size_t)(first + t0 + t) * p.v_stride + head * full + column0 + c];
     }
     __syncthreads();
     if (MODE == 0) {
@@ -229,9 +231,13 @@ gated_recurrence_kernel(RecurrenceArgs p, T* __restrict__ out) {
         }
         s_o[(slice * REC_CHUNK + t) * vdim + j] = o0 + o1;
       };
-      if (KD <= 32 && count == REC_CHUNK) {
-        // a full chunk: unrolled (not with 64 rows per thread: the registers run out), so that the next tokens' loads are issued under this token's arithmetic
-#pragma unroll
+      if (KD <= 8 && count == REC_CHUNK) {
+        // a full chunk: eight tokens at a time, so that the next tokens' loads are issued under this token's arithmetic
+#pragma unroll 8
+        for (int t = 0; t < REC_CHUNK; ++t) one_token(t);
+      } else if (KD <= 32 && count == REC_CHUNK) {
+        // more rows per thread: two tokens at a time (more would not fit the registers)
+#pragma unroll 2
         for (int t = 0; t < REC_CHUNK; ++t) one_token(t);
       } else {
         for (int t = 0; t < count; ++t) one_token(t);
@@ -242,16 +248,18 @@ gated_recurrence_kernel(RecurrenceArgs p, T* __restrict__ out) {
     for (int t = warp; t < count; t += warps) {
       float sq = 0.f;
       const float bonus = MODE == 0 ? s_bonus[t] : 0.f;
+      const size_t row = (size_t)(first + t0 + t);
       for (int c = lane; c < vdim; c += 32) {
         float o = 0.f;
         for (int s = 0; s < slices; ++s) o += s_o[(s * REC_CHUNK + t) * vdim + c];
         if (MODE == 0) o = fmaf(s_v[t * vdim + c], bonus, o);
+        if (p.raw_out != nullptr) p.raw_out[(row * p.heads + head) * full + column0 + c] = o;
         s_o[t * vdim + c] = o;      // slice 0's place now holds the sum (same lane reads it below)
         sq = fmaf(o, o, sq);
       }
+      if (p.raw_out != nullptr) continue;       // the value channels are spread over CTAs: finished elsewhere
       sq = warp_sum(sq);
       const float factor = 1.f / sqrtf(sq / (float)vdim + p.eps);
-      const size_t row = (size_t)(first + t0 + t);
       for (int c = lane; c < vdim; c += 32) {
         float y = s_o[t * vdim + c] * factor * p.weight[p.weight_per_head ? head * vdim + c : c];
         if (MODE == 0) {
@@ -266,8 +274,36 @@ gated_recurrence_kernel(RecurrenceArgs p, T* __restrict__ out) {
 #pragma unroll
     for (int i = 0; i < KD; ++i) {
       const int row = slice * KD + i;
-      if (row < dim) state[(size_t)row * vdim + j] = S[i];
+      if (row < dim) state[(size_t)row * full + j] = S[i];
     }
+  }
+}
+
+// The end of a recurrence whose value channels were spread over CTAs: one warp per (row, head) takes
+// o / rms(o) * weight (* silu(gate)).
+template <typename T>
+__global__ void __launch_bounds__(128)
+recurrence_finish_kernel(const float* raw, const float* gate, long long gate_stride, const float* __restrict__ weight,
+                         int weight_per_head, T* __restrict__ out, long long items, int heads, int vdim, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (item >= items) return;
+  const int lane = threadIdx.x & 31;
+  const long long row = item / heads;
+  const int head = (int)(item - row * heads);
+  const float* o = raw + (row * heads + head) * vdim;
+  float sq = 0.f;
+  for (int c = lane; c < vdim; c += 32) sq = fmaf(o[c], o[c], sq);
+  sq = warp_sum(sq);
+  const float factor = 1.f / sqrtf(sq / (float)vdim + eps);
+  for (int c = lane; c < vdim; c += 32) {
+    float y = o[c] * factor * weight[weight_per_head ? head * vdim + c : c];
+    if (gate != nullptr) {
+      const float g = gate[row * gate_stride + head * vdim + c];
+      y *= g / (1.f + expf(-g));
+    }
+    out[(row * heads + head) * vdim + c] = from_float<T>(y);
   }
 }
 
@@ -312,9 +348,17 @@ __global__ void tanh_kernel(T* x, long long count) {
   if (i < count) x[i] = from_float<T>(tanhf(to_float(x[i])));
 }
 
+// `raw`: float32 scratch [rows, heads*vdim], or null.  With it, and value heads of several times 32
+// channels, steps with long segments spread each head's value channels over CTAs of 32: more CTAs,
+// and threads that each hold fewer state rows (the recurrence is bound by the latency of its
+// per-token chain, not by throughput); the norm then runs as a second kernel.
 template <typename T, int MODE>
-int launch_recurrence(const RecurrenceArgs& args, void* out, int segments, cudaStream_t stream) {
-  const int vp = (args.vdim + 31) / 32 * 32;
+int launch_recurrence(RecurrenceArgs args, void* out, float* raw, int segments, int rows, int max_q_len,
+                      cudaStream_t stream) {
+  const bool spread = raw != nullptr && max_q_len >= 64 && args.vdim > 32 && args.vdim % 32 == 0;
+  args.columns = spread ? 32 : args.vdim;
+  args.raw_out = spread ? raw : nullptr;
+  const int vp = (args.columns + 31) / 32 * 32;
   // key channels per thread: the fewest of 8, 16, 32, 64 with which a CTA stays within 512 threads
   // (more threads with shorter chains hide the latency of the shared-memory loads that feed them)
   int kd = 8;
@@ -322,8 +366,8 @@ int launch_recurrence(const RecurrenceArgs& args, void* out, int segments, cudaS
   const int slices = (args.dim + kd - 1) / kd;
   if (vp * slices > 512) return MLR_TOO_LARGE;
   const int dim_pad = slices * kd;
-  const size_t shared = sizeof(float) * ((size_t)3 * REC_CHUNK * dim_pad + REC_CHUNK + (size_t)REC_CHUNK * args.vdim +
-                                         (size_t)slices * REC_CHUNK * args.vdim);
+  const size_t shared = sizeof(float) * ((size_t)3 * REC_CHUNK * dim_pad + REC_CHUNK + (size_t)REC_CHUNK * args.columns +
+                                         (size_t)slices * REC_CHUNK * args.columns);
   auto kernel = kd == 8 ? gated_recurrence_kernel<T, MODE, 8> : kd == 16 ? gated_recurrence_kernel<T, MODE, 16>
                 : kd == 32 ? gated_recurrence_kernel<T, MODE, 32> : gated_recurrence_kernel<T, MODE, 64>;
   if (shared > 200 * 1024) return MLR_TOO_LARGE;
@@ -331,7 +375,14 @@ int launch_recurrence(const RecurrenceArgs& args, void* out, int segments, cudaS
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (err != cudaSuccess) return (int)err;
   }
-  launch_kernel(kernel, dim3(args.heads, segments), dim3(vp, slices), shared, stream, args, (T*)out);
+  launch_kernel(kernel, dim3(args.heads, segments, args.vdim / args.columns), dim3(vp, slices), shared, stream, args,
+                (T*)out);
+  int status = launch_status();
+  if (status != MLR_OK || !spread) return status;
+  const long long items = (long long)rows * args.heads;
+  launch_kernel(recurrence_finish_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (const float*)raw,
+                MODE == 0 ? args.gate : (const float*)nullptr, args.gate_stride, args.weight, args.weight_per_head,
+                (T*)out, items, args.heads, args.vdim, args.eps);
   return launch_status();
 }
 
@@ -401,13 +452,15 @@ MLR_EXPORT int mlr_token_shift(const float* a, const float* coef, float* state, 
 // mode 0: bonus recurrence (r, k = b, v, decay raw, gate raw; aux = bonus [heads*dim]; weight [heads*vdim]).
 // mode 1: forget-gate recurrence (r = raw q, v, forget raw; aux = lower bound [heads*dim]; weight [vdim]).
 // All inputs float32 views with a row stride (in elements); state float32 [slots, heads, dim, vdim];
-// out: out_dtype [rows, heads*vdim].
+// out: out_dtype [rows, heads*vdim]; scratch: float32 of the same shape or null; rows: the step's
+// rows; max_q_len: its longest segment.
 MLR_EXPORT int mlr_gated_recurrence(int mode, const float* r, long long r_stride, const float* b, long long b_stride,
                                     const float* v, long long v_stride, const float* raw, long long raw_stride,
                                     const float* gate, long long gate_stride, const float* bias, const float* aux,
-                                    const float* weight, float eps, float* state, void* out, const int* seg_q_start,
-                                    const int* seg_q_len, const int* seg_slot, int segments, int heads, int dim,
-                                    int vdim, int out_dtype, cudaStream_t stream) {
+                                    const float* weight, float eps, float* state, void* out, float* scratch,
+                                    const int* seg_q_start, const int* seg_q_len, const int* seg_slot, int segments,
+                                    int rows, int max_q_len, int heads, int dim, int vdim, int out_dtype,
+                                    cudaStream_t stream) {
   if (segments == 0) return MLR_OK;
   if (segments < 0 || heads <= 0 || dim <= 0 || vdim <= 0) return MLR_BAD_SIZE;
   if (segments > 65535) return MLR_TOO_LARGE;
@@ -418,10 +471,10 @@ MLR_EXPORT int mlr_gated_recurrence(int mode, const float* r, long long r_stride
   args.bias = bias; args.aux = aux; args.weight = weight; args.eps = eps; args.state = state;
   args.seg_q_start = seg_q_start; args.seg_q_len = seg_q_len; args.seg_slot = seg_slot;
   args.heads = heads; args.dim = dim; args.vdim = vdim; args.weight_per_head = mode == 0 ? 1 : 0;
-  if (mode == 0 && out_dtype == MLR_F32) return launch_recurrence<float, 0>(args, out, segments, stream);
-  if (mode == 0 && out_dtype == MLR_BF16) return launch_recurrence<bf16, 0>(args, out, segments, stream);
-  if (mode == 1 && out_dtype == MLR_F32) return launch_recurrence<float, 1>(args, out, segments, stream);
-  if (mode == 1 && out_dtype == MLR_BF16) return launch_recurrence<bf16, 1>(args, out, segments, stream);
+  if (mode == 0 && out_dtype == MLR_F32) return launch_recurrence<float, 0>(args, out, scratch, segments, rows, max_q_len, stream);
+  if (mode == 0 && out_dtype == MLR_BF16) return launch_recurrence<bf16, 0>(args, out, scratch, segments, rows, max_q_len, stream);
+  if (mode == 1 && out_dtype == MLR_F32) return launch_recurrence<float, 1>(args, out, scratch, segments, rows, max_q_len, stream);
+  if (mode == 1 && out_dtype == MLR_BF16) return launch_recurrence<bf16, 1>(args, out, scratch, segments, rows, max_q_len, stream);
   return mode == 0 || mode == 1 ? MLR_BAD_DTYPE : MLR_BAD_SIZE;
 }
 

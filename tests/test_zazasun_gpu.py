@@ -247,3 +247,54 @@ def test_gated_product_with_the_gelu_epilogue(rows, inner, width):
     want = plain.gelu_tanh(x.double() @ gate.double().T) * (x.double() @ up.double().T)
     error = (got.double().cpu() - want).abs().max() / want.abs().max()
     assert float(error) < 1e-2
+
+
+def test_command_line_and_replay_program_with_a_model_folder(tmp_path):
+    """``make-random`` writes a Zazasun folder from a config.json, ``generate`` reproduces the plain
+    implementation's greedy tokens from it, and the replay program writes the logits of the wanted
+    places step by step, with pages and slots given back in between."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+
+    from mini_llm_runtime_b200.weights import read_checkpoint
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+
+    def cli(*arguments, stdin=None):
+        done = subprocess.run([sys.executable, *arguments], capture_output=True, text=True, env=env, timeout=600,
+                              input=stdin)
+        assert done.returncode == 0, done.stderr[-2000:]
+        return done.stdout
+
+    (tmp_path / "config.json").write_text(json.dumps(zs.ODD))
+    folder = tmp_path / "model"
+    cli("-m", "mini_llm_runtime_b200", "make-random", "--config", str(tmp_path / "config.json"), "--seed", "4",
+        "--out", str(folder))
+    tensors = read_checkpoint(folder)
+    prompt = zs.tokens_for(77, 11, 6)
+    sequence = list(prompt)
+    for _ in range(5):
+        sequence.append(int(torch.argmax(plain.forward(tensors, zs.ODD, sequence)[-1])))
+    record = json.loads(cli("-m", "mini_llm_runtime_b200", "generate", "--model", str(folder), "--dtype", "float32",
+                            "--max-model-len", "64", "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "5"
+                            ).splitlines()[-1])
+    assert record["generated_ids"] == sequence[len(prompt):]
+
+    other = zs.tokens_for(77, 30, 7)
+    steps = [{"step": 0, "entries": [{"id": "p", "tokens": prompt[:4], "want": [0, 3]}], "end": []},
+             {"step": 1, "entries": [{"id": "p", "tokens": prompt[4:], "want": [6]},
+                                     {"id": "o", "tokens": other, "want": [29]}], "end": ["p"]},
+             {"step": 2, "entries": [], "end": ["o"]}]
+    out = cli(os.path.join(root, "bin", "trace_run"), "--model", str(folder), "--dtype", "float32", "--out",
+              str(tmp_path / "logits"), "--max-tokens", "64", stdin="\n".join(json.dumps(s) for s in steps) + "\n")
+    assert [line for line in out.splitlines() if line.startswith("done")] == ["done 0", "done 1", "done 2"]
+    first = torch.from_numpy(np.fromfile(tmp_path / "logits" / "0.f32", dtype="<f4").reshape(2, 77))
+    second = torch.from_numpy(np.fromfile(tmp_path / "logits" / "1.f32", dtype="<f4").reshape(2, 77))
+    want = plain.forward(tensors, zs.ODD, prompt)
+    zs.assert_logits_close(torch.cat([first, second[:1]]), want[[0, 3, 10]], torch.float32)
+    zs.assert_logits_close(second[1:], plain.forward(tensors, zs.ODD, other)[29:], torch.float32)
