@@ -142,7 +142,8 @@ gated_recurrence_kernel(RecurrenceArgs p, T* __restrict__ out) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ __align__(16) float shared[];
-  const int dim = p.dim, vdim = p.columns, full = p.vdim, column0 = blockIdx.z * p.columns;
+  const int dim = p.dim, full = p.vdim, column0 = blockIdx.z * p.columns;
+  const int vdim = min(p.columns, full - column0);      // this CTA's value channels (the last part may be short)
   const int slices = blockDim.y, dim_pad = slices * KD;
   float* s_r = shared;                              // [CHUNK][dim_pad]
   float* s_a = s_r + REC_CHUNK * dim_pad;
@@ -355,16 +356,25 @@ __global__ void tanh_kernel(T* x, long long count) {
 template <typename T, int MODE>
 int launch_recurrence(RecurrenceArgs args, void* out, float* raw, int segments, int rows, int max_q_len,
                       cudaStream_t stream) {
-  const bool spread = raw != nullptr && max_q_len >= 64 && args.vdim > 32 && args.vdim % 32 == 0;
+  // threads a CTA needs for `columns` value channels, with the fewest key channels per thread (8, 16, 32
+  // or 64) that keep it within 512: more threads with shorter chains hide the latency of the
+  // shared-memory loads that feed them
+  auto plan = [&](int columns, int* kd_out) {
+    const int lanes = (columns + 31) / 32 * 32;
+    int kd = 8;
+    while (kd < 64 && lanes * ((args.dim + kd - 1) / kd) > 512) kd *= 2;
+    *kd_out = kd;
+    return lanes * ((args.dim + kd - 1) / kd);
+  };
+  int kd = 8;
+  const bool whole_fits = plan(args.vdim, &kd) <= 512;
+  // parts of 32 channels: in steps with long segments, and whenever a whole head does not fit a CTA
+  const bool spread = raw != nullptr && args.vdim > 32 && (max_q_len >= 64 || !whole_fits);
   args.columns = spread ? 32 : args.vdim;
   args.raw_out = spread ? raw : nullptr;
   const int vp = (args.columns + 31) / 32 * 32;
-  // key channels per thread: the fewest of 8, 16, 32, 64 with which a CTA stays within 512 threads
-  // (more threads with shorter chains hide the latency of the shared-memory loads that feed them)
-  int kd = 8;
-  while (kd < 64 && vp * ((args.dim + kd - 1) / kd) > 512) kd *= 2;
+  if (plan(args.columns, &kd) > 512) return MLR_TOO_LARGE;
   const int slices = (args.dim + kd - 1) / kd;
-  if (vp * slices > 512) return MLR_TOO_LARGE;
   const int dim_pad = slices * kd;
   const size_t shared = sizeof(float) * ((size_t)3 * REC_CHUNK * dim_pad + REC_CHUNK + (size_t)REC_CHUNK * args.columns +
                                          (size_t)slices * REC_CHUNK * args.columns);
@@ -375,7 +385,7 @@ int launch_recurrence(RecurrenceArgs args, void* out, float* raw, int segments, 
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (err != cudaSuccess) return (int)err;
   }
-  launch_kernel(kernel, dim3(args.heads, segments, args.vdim / args.columns), dim3(vp, slices), shared, stream, args,
+  launch_kernel(kernel, dim3(args.heads, segments, (args.vdim + args.columns - 1) / args.columns), dim3(vp, slices), shared, stream, args,
                 (T*)out);
   int status = launch_status();
   if (status != MLR_OK || !spread) return status;

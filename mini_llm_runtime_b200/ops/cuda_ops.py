@@ -855,9 +855,9 @@ class CudaOps:
             raise KernelError(f"state has shape {tuple(state.shape)}, expected [slots, {heads}, {dim}, {vdim}]")
         null = (ctypes.c_void_p(0), ctypes.c_longlong(0))
         out = torch.empty((rows, heads * vdim), dtype=out_dtype, device=r.device)
-        # steps with long segments spread a head's value channels over CTAs and finish in a second kernel
-        scratch = (torch.empty((rows, heads * vdim), dtype=torch.float32, device=r.device)
-                   if ctx.max_q_len >= 64 and vdim > 32 and vdim % 32 == 0 else None)
+        # steps with long segments, and heads too large for one CTA, spread a head's value channels
+        # over CTAs and finish in a second kernel, which reads the un-normalised rows from here
+        scratch = torch.empty((rows, heads * vdim), dtype=torch.float32, device=r.device) if vdim > 32 else None
         _check(build.load_library("sequence_mix").mlr_gated_recurrence(
             mode, *self._view(r, "r", rows, heads * dim), *(null if b is None else self._view(b, "b", rows, heads * dim)),
             *self._view(v, "v", rows, heads * vdim), *self._view(raw, "raw", rows, heads * dim),

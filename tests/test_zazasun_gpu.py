@@ -298,3 +298,16 @@ def test_command_line_and_replay_program_with_a_model_folder(tmp_path):
     want = plain.forward(tensors, zs.ODD, prompt)
     zs.assert_logits_close(torch.cat([first, second[:1]]), want[[0, 3, 10]], torch.float32)
     zs.assert_logits_close(second[1:], plain.forward(tensors, zs.ODD, other)[29:], torch.float32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_state_heads_larger_than_one_block_of_threads_holds(dtype):
+    """A 256 x 256 state per head, and value heads whose size is no multiple of 32: the recurrence
+    spreads the value channels over several blocks (in prompt steps always, in decode steps when a
+    head does not fit one block), the last part being short."""
+    config = zs.config([zs.wkv(1, 256), zs.hgrn2(1, 40, 200, ff=32)], width=64, vocab=60)
+    engine = zs.ZEngine(config, dtype, DEVICE, seed=8, long=True)
+    tokens = zs.tokens_for(60, 90, 4)
+    want = engine.plain(tokens)
+    zs.assert_logits_close(engine.run_cuts("a", tokens, []), want, dtype, "whole")
+    zs.assert_logits_close(engine.run_cuts("b", tokens, [70, 71, 72, 80]), want, dtype, "portions and single tokens")
