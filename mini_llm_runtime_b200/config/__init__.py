@@ -1,11 +1,13 @@
 from .qwen2 import Qwen2Config, qwen2_model_spec
 from .registry import (Architecture, architecture_of, config_from_dict, known_architectures,
                        load_config, register_architecture, unregister_architecture)
+from .rozesun import RozesunConfig, RozesunLayer, rozesun_model_spec
 from .spec import LayerSpec, ModelSpec, PartSpec, RunStep
 from .zazasun import ZazasunConfig, ZazasunLayer, zazasun_model_spec
 
 __all__ = [
-    "Architecture", "LayerSpec", "ModelSpec", "PartSpec", "Qwen2Config", "RunStep", "ZazasunConfig", "ZazasunLayer",
+    "Architecture", "LayerSpec", "ModelSpec", "PartSpec", "Qwen2Config", "RozesunConfig", "RozesunLayer",
+    "RunStep", "ZazasunConfig", "ZazasunLayer",
     "architecture_of", "config_from_dict", "known_architectures", "load_config",
-    "qwen2_model_spec", "register_architecture", "unregister_architecture", "zazasun_model_spec",
+    "qwen2_model_spec", "register_architecture", "rozesun_model_spec", "unregister_architecture", "zazasun_model_spec",
 ]

@@ -14,6 +14,7 @@ from pathlib import Path
 from typing import Any, Callable, Mapping
 
 from .qwen2 import Qwen2Config, qwen2_model_spec
+from .rozesun import RozesunConfig, rozesun_model_spec
 from .spec import ModelSpec
 from .zazasun import ZazasunConfig, zazasun_model_spec
 
@@ -81,3 +82,4 @@ def load_config(model_dir: str | Path):
 
 register_architecture(Qwen2Config.architecture, Qwen2Config.from_dict, qwen2_model_spec)
 register_architecture(ZazasunConfig.architecture, ZazasunConfig.from_dict, zazasun_model_spec)
+register_architecture(RozesunConfig.architecture, RozesunConfig.from_dict, rozesun_model_spec)

@@ -40,7 +40,8 @@ class LayerSpec:
 class RunStep:
     """One entry of the run order.
 
-    ``layer`` indexes ``ModelSpec.layers`` (a layer may be named twice).  ``cache`` names the
+    ``layer`` indexes ``ModelSpec.layers`` (a layer may be named twice: a run of layers passed
+    through several times with the same weights has one run step, and one cache entry, per pass).  ``cache`` names the
     cache entry the mixer uses; two run steps with the same ``cache`` share it, and a step
     with ``writes_cache=False`` only reads what an earlier step wrote there.
     """
@@ -48,6 +49,7 @@ class RunStep:
     layer: int
     cache: int
     writes_cache: bool = True
+    offset_row: int | None = None     # row of the model's offset table added to the stream before the layer
 
 
 @dataclass(frozen=True)
@@ -61,6 +63,7 @@ class ModelSpec:
     run_order: tuple[RunStep, ...]
     final_norm: PartSpec
     head: PartSpec
+    offsets: PartSpec | None = None     # table of vectors that run steps add to the stream (``RunStep.offset_row``)
 
     def __post_init__(self) -> None:
         if not self.layers or not self.run_order:
@@ -72,6 +75,8 @@ class ModelSpec:
                                  f"but the model has {len(self.layers)} layers")
             if step.cache < 0:
                 raise ValueError(f"run step {position} has a negative cache entry")
+            if step.offset_row is not None and self.offsets is None:
+                raise ValueError(f"run step {position} asks for an offset, but the model has no offset table")
             if step.writes_cache:
                 if step.cache in writers:
                     raise ValueError(f"cache entry {step.cache} is written by run steps "

@@ -90,6 +90,8 @@ class ContinuousBatchEngine:
         self._next_buffer = 0
 
     # ------------------------------------------------------------------ assembly
+    DEFAULT_MODEL_LEN = 32768
+
     @classmethod
     def from_model(cls, model: DecoderModel, *, block_size: int = 16, total_blocks: int | None = None,
                    max_running_requests: int = 8, max_batch_tokens: int = 2048,
@@ -97,7 +99,9 @@ class ContinuousBatchEngine:
                    batching_policy: BatchingPolicy = BatchingPolicy.CONTINUOUS,
                    chunked_prefill: bool = True, enable_nvtx: bool = False,
                    step_ahead: bool = False) -> "ContinuousBatchEngine":
-        max_model_len = min(max_model_len or model.spec.max_positions, model.spec.max_positions)
+        # a model without a position limit of its own gets this engine's default
+        max_model_len = min(max_model_len or min(model.spec.max_positions, cls.DEFAULT_MODEL_LEN),
+                            model.spec.max_positions)
         if total_blocks is None:
             total_blocks = max_running_requests * -(-max_model_len // block_size)
         cache = CacheManager(model.cache_needs(), page_size=block_size, num_pages=total_blocks,

@@ -13,7 +13,7 @@ from typing import Mapping
 import torch
 
 from ..config.spec import ModelSpec
-from ..parts.base import Block, KVCacheNeed, StateNeed, TensorSpec, build_part, part_factory
+from ..parts.base import Block, KVCacheNeed, PendingDelta, StateNeed, TensorSpec, build_part, part_factory
 from ..weights.loader import check_tensors
 
 
@@ -36,6 +36,7 @@ class DecoderModel:
                 None if layer.feed_forward_norm is None else build_part("norm", layer.feed_forward_norm, compute_dtype),
                 **({"extras": extras} if extras else {}),
             ))
+        self.offsets = None if spec.offsets is None else build_part("offset", spec.offsets, compute_dtype)
         self.final_norm = build_part("norm", spec.final_norm, compute_dtype)
         self.head = build_part("head", spec.head, compute_dtype)
         self.device: torch.device | None = None
@@ -45,6 +46,8 @@ class DecoderModel:
         yield self.embedding
         for block in self.blocks:
             yield from block.parts()
+        if self.offsets is not None:
+            yield self.offsets
         yield self.final_norm
         yield self.head
 
@@ -92,7 +95,16 @@ class DecoderModel:
         pending = None
         for step in self.spec.run_order:
             view = ctx.cache_view(step.cache)
-            residual, pending = self.blocks[step.layer].forward(residual, pending, ctx, view, step.writes_cache)
+            block = self.blocks[step.layer]
+            if step.offset_row is None:
+                residual, pending = block.forward(residual, pending, ctx, view, step.writes_cache)
+            elif block.takes_offset:
+                residual, pending = block.forward(residual, pending, ctx, view, step.writes_cache,
+                                                  offset=self.offsets.vector(step.offset_row))
+            else:
+                residual = self._settle(residual, pending)
+                residual = ctx.ops.add_rows(residual, self.offsets.vector(step.offset_row))
+                residual, pending = block.forward(residual, None, ctx, view, step.writes_cache)
         if ctx.num_wanted == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=residual.device)
         k = ctx.ops
@@ -101,7 +113,22 @@ class DecoderModel:
         if pending is None:
             normed = self.final_norm.forward(rows)
         else:
-            delta = pending if everything else k.gather_rows(pending, ctx.wanted_rows)
+            post = pending.norm if isinstance(pending, PendingDelta) else None
+            delta = pending.tensor if isinstance(pending, PendingDelta) else pending
+            delta = delta if everything else k.gather_rows(delta, ctx.wanted_rows)
             # the stream itself must stay as it is only if it is read again; it is not after the last layer
-            normed = self.final_norm.add_forward(rows, delta)
+            normed = (self.final_norm.add_forward(rows, delta) if post is None
+                      else self.final_norm.add_forward(rows, delta, post=post))
         return self.head.forward(normed, self.embedding)
+
+    @staticmethod
+    def _settle(residual, pending):
+        """Add what is still pending into the stream."""
+        if pending is None:
+            return residual
+        if isinstance(pending, PendingDelta):
+            if pending.norm is not None:
+                return pending.norm.add_into(residual, pending.tensor)
+            pending = pending.tensor
+        from .. import ops
+        return ops.current().add_inplace(residual, pending)

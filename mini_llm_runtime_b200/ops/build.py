@@ -45,6 +45,8 @@ LIBRARIES: dict[str, tuple[str, ...]] = {
     "sequence_mix": (),
     "attention_diff": (),
     "attention_diff_mma": (),
+    "stream32": (),
+    "attention_latent": (),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -996,6 +996,196 @@ class CudaOps:
                 "differential attention")
         return out
 
+    # ------------------------------------------------------------------ 32-bit stream with layer norms
+    def embedding_rows32(self, ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+        """float32 rows table[ids] of a table in the compute dtype."""
+        _need(ids, "ids", torch.int32, 1)
+        _need(table, "table", dims=2)
+        out = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
+        _check(build.load_library("stream32").mlr_embedding_rows32(
+            _ptr(ids), _ptr(table), _ptr(out), ids.shape[0], table.shape[1], table.shape[0], _code(table.dtype),
+            _stream()), "embedding_rows32")
+        return out
+
+    def layer_norm_step(self, x: torch.Tensor, eps: float, *, delta: torch.Tensor | None = None, delta_norm=None,
+                        offset: torch.Tensor | None = None, norm=None, out_dtype: torch.dtype | None = None):
+        """One pass over the rows of the float32 stream ``x`` [rows, width] that does, in this order,
+        what is given: x += LN(delta; *delta_norm) (``delta`` float32, ``delta_norm`` = (weight, bias)),
+        x += offset (a float32 vector), and returns LN(x; *norm) in ``out_dtype`` (None without
+        ``norm``).  LN(v; w, b) = (v - mean) / sqrt(variance + eps) * w + b."""
+        _need(x, "x", torch.float32, 2)
+        rows, width = x.shape
+        vectors = []
+        for name, pair in (("delta_norm", delta_norm), ("norm", norm)):
+            if pair is None:
+                vectors += [None, None]
+                continue
+            for vector in pair:
+                _need(vector, name, torch.float32, 1)
+                if vector.shape[0] != width:
+                    raise KernelError(f"{name} holds {vector.shape[0]} entries, rows have {width}")
+                vectors.append(vector)
+        if delta is not None:
+            _need(delta, "delta", torch.float32, 2)
+            if delta.shape != x.shape or delta_norm is None:
+                raise KernelError("delta needs the stream's shape and its own norm's weight and bias")
+        if offset is not None:
+            _need(offset, "offset", torch.float32, 1)
+            if offset.shape[0] != width:
+                raise KernelError("the offset vector needs one entry per column")
+        out = None
+        if norm is not None:
+            out = torch.empty((rows, width), dtype=out_dtype or torch.float32, device=x.device)
+        _check(build.load_library("stream32").mlr_layer_norm_step(
+            _ptr(x), _ptr(delta), _ptr(vectors[0]), _ptr(vectors[1]), _ptr(offset), _ptr(vectors[2]), _ptr(vectors[3]),
+            _ptr(out), rows, width, ctypes.c_float(eps), _code(out.dtype if out is not None else torch.float32),
+            _stream()), "layer_norm_step")
+        return out
+
+    def add_rows(self, x: torch.Tensor, vector: torch.Tensor) -> torch.Tensor:
+        """x[r] += vector for every row of a float32 x, in place."""
+        self.layer_norm_step(x, 0.0, offset=vector)
+        return x
+
+    def clamped_gate(self, gate_up: torch.Tensor, block: int, limit: float, slope: float) -> torch.Tensor:
+        """g * sigmoid(slope * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), on rows of
+        blocks of ``block`` gate values followed by their up values."""
+        _need(gate_up, "gate_up", dims=2)
+        inner = gate_up.shape[1] // 2
+        if gate_up.shape[1] % 2 or block <= 0 or inner % block:
+            raise KernelError("gate_up rows must hold gate and up blocks of equal width")
+        out = torch.empty((gate_up.shape[0], inner), dtype=gate_up.dtype, device=gate_up.device)
+        _check(build.load_library("stream32").mlr_clamped_gate(
+            _ptr(gate_up), _ptr(out), ctypes.c_longlong(gate_up.shape[0]), inner, int(block), ctypes.c_float(limit),
+            ctypes.c_float(slope), _code(gate_up.dtype), _stream()), "clamped_gate")
+        return out
+
+    def linear_clamped_gate(self, x: torch.Tensor, weight: torch.Tensor, block: int, limit: float, slope: float) -> torch.Tensor:
+        """The clamped gate of (x Wg^T, x Wu^T) for ``weight`` [2*inner, K] of interleaved gate/up blocks."""
+        return self.clamped_gate(self.linear(x, weight), block, limit, slope)
+
+    def scale_(self, x: torch.Tensor, factor: float) -> torch.Tensor:
+        """x *= factor in place (float32)."""
+        _need(x, "x", torch.float32)
+        _check(build.load_library("stream32").mlr_scale_inplace(
+            _ptr(x), ctypes.c_longlong(x.numel()), ctypes.c_float(factor), _stream()), "scale")
+        return x
+
+    # ------------------------------------------------------------------ latent attention
+    def latent_prepare(self, down: torch.Tensor, q_at: int, q_rank: int, c_at: int, rank: int, rot: int,
+                       q_weight: torch.Tensor, c_weight: torch.Tensor, eps: float, positions: torch.Tensor,
+                       frequencies: torch.Tensor, interleaved: bool, slots: torch.Tensor, pool: torch.Tensor,
+                       write: bool = True) -> torch.Tensor:
+        """From the float32 product ``down`` [rows, n]: the RMS-normalised query latent (columns
+        q_at .. q_at + q_rank, returned in the pool's dtype), and into the cache at ``slots`` the
+        RMS-normalised latent (columns c_at .. c_at + rank) followed by the next ``rot`` columns with
+        their first 2 * len(frequencies) entries turned by the rows' positions."""
+        _need(down, "down", torch.float32, 2)
+        _need(q_weight, "q_weight", torch.float32, 1)
+        _need(c_weight, "c_weight", torch.float32, 1)
+        _need(positions, "positions", torch.int32, 1)
+        _need(frequencies, "frequencies", torch.float32, 1)
+        _need(slots, "slots", torch.int64, 1)
+        _need(pool, "pool", None, 4)
+        rows = down.shape[0]
+        if (q_at < 0 or c_at < 0 or q_at + q_rank > down.shape[1] or c_at + rank + rot > down.shape[1]
+                or q_weight.shape[0] != q_rank or c_weight.shape[0] != rank):
+            raise KernelError("column ranges or norm weights do not fit the product")
+        if pool.shape[1] != 1 or pool.shape[3] != rank + rot or slots.shape[0] != rows or positions.shape[0] != rows:
+            raise KernelError(f"pool has shape {tuple(pool.shape)}, expected [pages, 1, page_size, {rank + rot}]; "
+                              "one slot and one position per row")
+        q_latent = torch.empty((rows, q_rank), dtype=pool.dtype, device=down.device)
+        _check(build.load_library("attention_latent").mlr_latent_prepare(
+            _ptr(down), ctypes.c_longlong(down.stride(0)), q_at, q_rank, c_at, rank, rot, _ptr(q_weight), _ptr(c_weight),
+            _ptr(positions), _ptr(frequencies), frequencies.shape[0], int(bool(interleaved)), _ptr(slots), _ptr(q_latent),
+            _ptr(pool), rows, ctypes.c_float(eps), int(bool(write)), _code(pool.dtype), _stream()), "latent_prepare")
+        return q_latent
+
+    def _head_linear(self, x, x_head, weight, heads, n, k, kn, out, out_head, mode=0, tail=0, positions=None,
+                     frequencies=None, interleaved=False, gate=None, gate_per_head=False):
+        rows = x.shape[0]
+        if (not isinstance(x, torch.Tensor) or not x.is_cuda or x.dtype != torch.float32 or x.dim() != 2
+                or x.stride(1) != 1):
+            raise KernelError("x must be a float32 CUDA view with unit column stride")
+        _need(weight, "weight", None, 2)
+        _need(out, "out", None, 2)
+        if weight.shape != ((heads * k, n) if kn else (heads * n, k)):
+            raise KernelError(f"weight has shape {tuple(weight.shape)}, which does not fit {heads} heads of {n} x {k}")
+        gate_ptr, gate_row = ctypes.c_void_p(0), ctypes.c_longlong(0)
+        if gate is not None:
+            if gate.dtype != torch.float32 or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape[0] != rows \
+                    or gate.shape[1] != (heads if gate_per_head else heads * n):
+                raise KernelError("gate must be a float32 view [rows, heads] or [rows, heads * n]")
+            gate_ptr, gate_row = _ptr(gate), ctypes.c_longlong(gate.stride(0))
+        pairs = 0 if frequencies is None else frequencies.shape[0]
+        _check(build.load_library("attention_latent").mlr_head_linear(
+            _ptr(x), ctypes.c_longlong(x.stride(0)), x_head, _ptr(weight), _ptr(out), ctypes.c_longlong(out.stride(0)),
+            out_head, rows, heads, n, k, int(kn), mode, tail, pairs, int(bool(interleaved)), _ptr(positions),
+            _ptr(frequencies), gate_ptr, gate_row, int(bool(gate_per_head)), _code(weight.dtype), _code(out.dtype),
+            _stream()), "head_linear")
+        return out
+
+    def absorb_queries(self, q: torch.Tensor, weight: torch.Tensor, heads: int, dim: int, rot: int, rank: int,
+                       positions: torch.Tensor, frequencies: torch.Tensor, interleaved: bool) -> torch.Tensor:
+        """Queries into the latent space.  q: float32 [rows, heads * (dim + rot)], per head [plain | to be
+        turned]; weight [heads * dim, rank] (the per-head key matrix).  Returns, in the weight's dtype,
+        [rows, heads * (rank + rot)]: per head weight_h^T q_plain followed by the turned part."""
+        _need(positions, "positions", torch.int32, 1)
+        _need(frequencies, "frequencies", torch.float32, 1)
+        if q.shape[1] != heads * (dim + rot) or 2 * frequencies.shape[0] > rot:
+            raise KernelError("q does not match the head count and sizes")
+        out = torch.empty((q.shape[0], heads * (rank + rot)), dtype=weight.dtype, device=q.device)
+        return self._head_linear(q, dim + rot, weight, heads, rank, dim, True, out, rank + rot, mode=1, tail=rot,
+                                 positions=positions, frequencies=frequencies, interleaved=interleaved)
+
+    def latent_values(self, mixed: torch.Tensor, weight: torch.Tensor, heads: int, vdim: int, rank: int,
+                      gate: torch.Tensor, gate_per_head: bool) -> torch.Tensor:
+        """Per head weight_h [vdim, rank] applied to the attention's latent sums (mixed: float32
+        [rows, heads * rank]), times sigmoid(gate) (float32 [rows, heads * vdim], or [rows, heads]
+        with ``gate_per_head``).  Returns [rows, heads * vdim] in the weight's dtype."""
+        if mixed.shape[1] != heads * rank:
+            raise KernelError("mixed does not match the head count and latent size")
+        out = torch.empty((mixed.shape[0], heads * vdim), dtype=weight.dtype, device=mixed.device)
+        return self._head_linear(mixed, rank, weight, heads, vdim, rank, False, out, vdim, mode=2, gate=gate,
+                                 gate_per_head=gate_per_head)
+
+    use_latent_decode_kernel = True
+
+    def latent_attention(self, q: torch.Tensor, pool: torch.Tensor, batch: AttentionBatch, heads: int, rank: int,
+                         rot: int, scale: float, window: int, sink: torch.Tensor | None) -> torch.Tensor:
+        """Attention of absorbed queries q [rows, heads * (rank + rot)] over cache rows [latent | turned key
+        part] that all heads share; the values are the latents.  Returns float32 [rows, heads * rank].
+        Key j is visible from position i if j <= i and (window == 0 or i - j < window); with ``sink``
+        (float32 [heads]) exp(sink) joins each head's softmax denominator."""
+        _need(q, "q", dims=2)
+        _need(pool, "pool", q.dtype, 4)
+        if q.shape[1] != heads * (rank + rot) or pool.shape[1] != 1 or pool.shape[3] != rank + rot:
+            raise KernelError("q or the cache rows do not match the head sizes")
+        if sink is not None:
+            _need(sink, "sink", torch.float32, 1)
+            if sink.shape[0] != heads:
+                raise KernelError("one sink per head")
+        if "tile_seg" not in batch.plan:
+            raise KernelError("the batch carries no attention work lists (plan_attention)")
+        out = torch.empty((q.shape[0], heads * rank), dtype=torch.float32, device=q.device)
+        lib = build.load_library("attention_latent")
+        tail = (heads, rank, rot, pool.shape[2], int(window or 0), ctypes.c_float(scale), _ptr(sink), _code(q.dtype),
+                _stream())
+        tiles = batch.counts["tiles"]
+        if self.use_latent_decode_kernel and batch.num_decode > 0:
+            listed = None if batch.num_decode == batch.num_segments else batch.plan["decode_seg"]
+            _check(lib.mlr_latent_attention_decode(
+                _ptr(q), _ptr(pool), _ptr(out), _ptr(listed), batch.num_decode, _ptr(batch.seg_q_start),
+                _ptr(batch.seg_pos0), _ptr(batch.block_table), _ptr(batch.seg_slot), batch.block_table.shape[1], *tail),
+                "latent attention (decode)")
+            tiles -= batch.num_decode       # the one-row segments' tiles are the last of the list
+        if tiles > 0:
+            _check(lib.mlr_latent_attention(
+                _ptr(q), _ptr(pool), _ptr(out), _ptr(batch.plan["tile_seg"]), _ptr(batch.plan["tile_row0"]),
+                _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0), _ptr(batch.block_table),
+                _ptr(batch.seg_slot), batch.block_table.shape[1], tiles, *tail), "latent attention")
+        return out
+
     # ------------------------------------------------------------------ sampling
     def sample(self, logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch.Tensor,
                counters: torch.Tensor) -> torch.Tensor:

@@ -8,6 +8,7 @@ needs, receives them, and computes on the rows of one step.  Five kinds exist:
 * ``norm``             normalises rows; also offers the fused "add to the residual, then norm"
 * ``position``         position encoding, used by a mixer as a component
 * ``shift``            blends each row with the row of the token before it (carried per request)
+* ``offset``           learned vectors added to the residual stream at chosen places of the run order
 * ``embedding`` / ``head``  token ids to rows, rows to logits
 
 plus ``block``, the arrangement of a layer's parts.  A part never learns which model it is in;
@@ -24,7 +25,7 @@ import torch
 
 from ..config.spec import PartSpec
 
-CATEGORIES = ("mixer", "feed_forward", "norm", "position", "shift", "embedding", "head", "block")
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "shift", "offset", "embedding", "head", "block")
 
 
 @dataclass(frozen=True)
@@ -56,7 +57,7 @@ class KVCacheNeed:
     num_kv_heads: int
     head_dim: int
     window: int | None = None
-    value_dim: int | None = None
+    value_dim: int | None = None      # 0: no values are stored (a mixer whose values are part of its key rows)
     keep_first: int = 0
 
     @property
@@ -207,6 +208,27 @@ class Shift(Part):
         raise NotImplementedError
 
 
+class StreamOffsets(Part):
+    """A table of learned vectors, one of which a run step may ask to be added to every row of the
+    residual stream before its layer runs (``RunStep.offset_row``)."""
+
+    category = "offset"
+
+    def vector(self, row: int) -> torch.Tensor:
+        """Vector ``row`` in the stream's dtype, on the device."""
+        raise NotImplementedError
+
+
+@dataclass
+class PendingDelta:
+    """A sublayer's output that is still to be added to the residual stream, with the norm it has
+    to pass on its way in (None: added as it is).  Blocks hand it on so that the add can share a
+    kernel with the next norm."""
+
+    tensor: torch.Tensor
+    norm: "Norm | None" = None
+
+
 class Head(Part):
     category = "head"
 
@@ -240,9 +262,14 @@ class Block:
     def finish_load(self, compute_dtype: torch.dtype) -> None:
         """Called once all four parts hold their tensors; an arrangement may fuse across them."""
 
-    def forward(self, residual: torch.Tensor, pending: torch.Tensor | None, ctx, view,
-                writes_cache: bool) -> tuple[torch.Tensor, torch.Tensor | None]:
-        """Takes and returns (residual stream, output not yet added to it)."""
+    # True: ``forward`` accepts ``offset=`` (a vector to add to the stream before the layer) and
+    # fuses the add into its first norm; otherwise the model adds the vector itself
+    takes_offset = False
+
+    def forward(self, residual: torch.Tensor, pending, ctx, view,
+                writes_cache: bool) -> tuple[torch.Tensor, "torch.Tensor | PendingDelta | None"]:
+        """Takes and returns (residual stream, output not yet added to it: a tensor or a
+        ``PendingDelta``)."""
         raise NotImplementedError
 
 

@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import Block, register_part
+from .base import Block, PendingDelta, register_part
 
 
 class PreNormResidual(Block):
@@ -74,5 +74,33 @@ class ParallelShifted(Block):
         return kernels.add_residual(residual, mixed, passed), None
 
 
+class SandwichNorm(Block):
+    """A norm before and one behind each sublayer: x <- x + post1(mixer(pre1(x))), then
+    x <- x + post2(ff(pre2(x))); a layer without a feed-forward ends after the first.  The two norms
+    behind the sublayers are the layer's further parts ``mixer_post_norm`` and ``feed_forward_post_norm``.
+    The stream x is 32-bit floats; the sublayers hand back 32-bit rows.  Each "add the normalised
+    output, then norm for the next sublayer" is one pass over the stream: the last output of the
+    layer travels on as a ``PendingDelta`` and is added by the next layer's first norm (or the
+    model's final norm), together with a vector the run order may ask to be added before the layer."""
+
+    takes_offset = True
+
+    def forward(self, residual, pending, ctx, view, writes_cache, offset=None):
+        kernels = ops.current()
+        if pending is None:
+            normed = self.mixer_norm.forward(residual, offset=offset)
+        elif isinstance(pending, PendingDelta):
+            normed = self.mixer_norm.add_forward(residual, pending.tensor, post=pending.norm, offset=offset)
+        else:
+            normed = self.mixer_norm.add_forward(residual, pending, offset=offset)
+        mixed = self.mixer.forward(normed, ctx, view, writes_cache)
+        if self.feed_forward is None:
+            return residual, PendingDelta(mixed, self.extras["mixer_post_norm"])
+        normed = self.feed_forward_norm.add_forward(residual, mixed, post=self.extras["mixer_post_norm"])
+        passed = self.feed_forward.forward(normed, ctx)
+        return residual, PendingDelta(passed, self.extras["feed_forward_post_norm"])
+
+
 register_part("block", "pre_norm_residual", PreNormResidual)
+register_part("block", "sandwich_norm", SandwichNorm)
 register_part("block", "parallel_shifted", ParallelShifted)

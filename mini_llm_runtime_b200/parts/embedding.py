@@ -21,15 +21,21 @@ class TokenEmbedding(Embedding):
         super().__init__(spec, compute_dtype)
         self.vocab_size = int(self.args["vocab_size"])
         self.hidden_size = int(self.args["hidden_size"])
+        # ``tensor``: the table's checkpoint name; ``rows="float32"``: hand out 32-bit rows (for a
+        # model whose residual stream is 32-bit), the table itself stays in the compute dtype
+        self.tensor = self.args.get("tensor") or self.prefix + "weight"
+        self.float_rows = str(self.args.get("rows", "")) == "float32"
         self.weight: torch.Tensor | None = None
 
     def tensors(self):
-        return {self.prefix + "weight": TensorSpec((self.vocab_size, self.hidden_size))}
+        return {self.tensor: TensorSpec((self.vocab_size, self.hidden_size))}
 
     def load(self, tensors, device):
-        self.weight = self._to_compute(tensors[self.prefix + "weight"], device)
+        self.weight = self._to_compute(tensors[self.tensor], device)
 
     def forward(self, token_ids, positions=None):
+        if self.float_rows:
+            return ops.current().embedding_rows32(token_ids, self.weight)
         return ops.current().embedding(token_ids, self.weight)
 
 
@@ -45,8 +51,12 @@ class TiedHead(Head):
         self.vocab_size = int(self.args["vocab_size"])
         self.hidden_size = int(self.args["hidden_size"])
         self.tied_to = self.args.get("tied_to")
+        self.scale = float(self.args.get("scale", 1.0))      # logits are multiplied by it (in 32-bit)
+        self.own_copy = bool(self.args.get("own_copy", True))   # False: the checkpoint never carries a copy
 
     def tensors(self):
+        if not self.own_copy:
+            return {}
         return {self.prefix + "weight": TensorSpec((self.vocab_size, self.hidden_size), optional=True)}
 
     def load(self, tensors, device):
@@ -60,7 +70,8 @@ class TiedHead(Head):
         return (self.tied_to,) if self.tied_to else ()
 
     def forward(self, x, embedding):
-        return ops.current().linear(x, embedding.weight, None, out_dtype=torch.float32)
+        logits = ops.current().linear(x, embedding.weight, None, out_dtype=torch.float32)
+        return logits if self.scale == 1.0 else ops.current().scale_(logits, self.scale)
 
 
 class LinearHead(Head):

@@ -59,7 +59,9 @@ class SwiGLU(FeedForward):
 
 class GatedMLP(FeedForward):
     """down(act(gate(x)) * up(x)) without biases, ``activation`` being ``silu`` or ``gelu_tanh``
-    (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).  The result leaves in 32-bit floats, for
+    (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))); or, with ``activation="clamped_swish"``,
+    down(g * sigmoid(slope * g) * (u + 1)) where g = min(gate(x), limit) and u = clamp(up(x), -limit,
+    limit) (``limit`` from the spec, ``slope`` 1.702 unless given).  The result leaves in 32-bit floats, for
     arrangements that sum into a 32-bit stream.  ``names`` gives the three checkpoint names after
     the prefix.  gate and up are stacked like SwiGLU's."""
 
@@ -70,8 +72,12 @@ class GatedMLP(FeedForward):
         self.hidden_size = int(self.args["hidden_size"])
         self.intermediate_size = int(self.args["intermediate_size"])
         self.activation = str(self.args.get("activation", "silu"))
-        if self.activation not in ("silu", "gelu_tanh"):
+        if self.activation not in ("silu", "gelu_tanh", "clamped_swish"):
             raise ValueError(f"unknown gate activation {self.activation!r}")
+        self.limit = float(self.args.get("limit", 0.0))
+        self.slope = float(self.args.get("slope", 1.702))
+        if self.activation == "clamped_swish" and not self.limit > 0:
+            raise ValueError("the clamped gate needs a positive limit")
         self.names = tuple(self.args.get("names") or ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
         self.w_gate_up = self.w_down = None
         self.block = self.intermediate_size
@@ -95,7 +101,10 @@ class GatedMLP(FeedForward):
 
     def forward(self, x, ctx):
         k = ops.current()
-        hidden = k.linear_gated(x, self.w_gate_up, self.block, self.activation)
+        if self.activation == "clamped_swish":
+            hidden = k.linear_clamped_gate(x, self.w_gate_up, self.block, self.limit, self.slope)
+        else:
+            hidden = k.linear_gated(x, self.w_gate_up, self.block, self.activation)
         return k.linear(hidden, self.w_down, out_dtype=torch.float32)
 
 

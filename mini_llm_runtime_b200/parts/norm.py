@@ -65,5 +65,61 @@ class ScalarRMSNorm(Norm):
         return ops.current().scalar_rms_norm(x, self.gain, self.eps, self.compute_dtype, want_float=True)
 
 
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(variance + eps) * w + b over each row, the variance being the mean of the
+    squared deviations; statistics, weight and bias in 32-bit.  It reads 32-bit rows.  Three uses, all
+    one pass of the same kernel over a 32-bit residual stream:
+
+    * ``forward(x)``: the normalised rows in the compute dtype (the input of a sublayer);
+    * ``add_into(stream, delta)``: stream += LN(delta), for a norm that sits behind a sublayer;
+    * ``add_forward(stream, delta, post=, offset=)``: stream += delta (normalised by ``post`` first,
+      if given), stream += offset (a vector, if given), then this norm of the new stream.
+
+    The checkpoint names come from the spec: ``tensor`` (weight) and ``tensor`` + ".b" (bias), unless
+    ``bias_tensor`` names it."""
+
+    graph_safe = True
+
+    def __init__(self, spec, compute_dtype):
+        super().__init__(spec, compute_dtype)
+        self.size = int(self.args["size"])
+        self.eps = float(self.args["eps"])
+        self.tensor = self.args.get("tensor") or self.prefix + "weight"
+        self.bias_tensor = self.args.get("bias_tensor") or self.tensor + ".b"
+        self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+
+    def tensors(self):
+        return {self.tensor: TensorSpec((self.size,), init="norm"),
+                self.bias_tensor: TensorSpec((self.size,), init="bias")}
+
+    def load(self, tensors, device):
+        self.weight = tensors[self.tensor].to(device=device, dtype=torch.float32).contiguous()
+        self.bias = tensors[self.bias_tensor].to(device=device, dtype=torch.float32).contiguous()
+
+    @property
+    def pair(self):
+        return self.weight, self.bias
+
+    def forward(self, x, offset=None):
+        return ops.current().layer_norm_step(x, self.eps, offset=offset, norm=self.pair, out_dtype=self.compute_dtype)
+
+    def add_into(self, stream, delta):
+        ops.current().layer_norm_step(stream, self.eps, delta=delta, delta_norm=self.pair)
+        return stream
+
+    def add_forward(self, residual, delta, post=None, offset=None):
+        if post is None:
+            ops.current().add_residual(residual, delta)
+            delta = None
+        elif post.eps != self.eps:
+            post.add_into(residual, delta)
+            delta = None
+        return ops.current().layer_norm_step(residual, self.eps, delta=delta,
+                                             delta_norm=None if delta is None else post.pair, offset=offset,
+                                             norm=self.pair, out_dtype=self.compute_dtype)
+
+
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "layer_norm", LayerNorm)
 register_part("norm", "scalar_rms_norm", ScalarRMSNorm)

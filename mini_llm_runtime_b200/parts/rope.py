@@ -17,6 +17,7 @@ from .base import PositionEncoding, register_part
 
 class RotateHalfRope(PositionEncoding):
     graph_safe = True
+    interleaved = False      # pair i is (i, i + head_dim/2)
 
     def __init__(self, spec, compute_dtype):
         super().__init__(spec, compute_dtype)
@@ -24,9 +25,12 @@ class RotateHalfRope(PositionEncoding):
         self.theta = float(self.args["theta"])
         if self.head_dim % 2:
             raise ValueError("rotate-half position encoding needs an even head_dim")
-        exponents = torch.arange(0, self.head_dim, 2, dtype=torch.float32) / self.head_dim
-        self._inv_freq_cpu = 1.0 / (self.theta ** exponents)
+        self._inv_freq_cpu = self._frequencies()
         self.inv_freq: torch.Tensor | None = None
+
+    def _frequencies(self) -> torch.Tensor:
+        exponents = torch.arange(0, self.head_dim, 2, dtype=torch.float32) / self.head_dim
+        return 1.0 / (self.theta ** exponents)
 
     def load(self, tensors, device):
         self.inv_freq = self._inv_freq_cpu.to(device)
@@ -41,4 +45,26 @@ class RotateHalfRope(PositionEncoding):
         return self.inv_freq
 
 
+class PairedRope(RotateHalfRope):
+    """The same rotation for mixers that turn a vector of ``head_dim`` numbers themselves (their
+    kernels take ``rotary_frequencies()`` and ``interleaved``): pair i is (i, i + head_dim/2), or, with
+    ``layout="interleaved"``, (2i, 2i + 1); it turns by position * theta^(-2i/head_dim).  The frequencies
+    are evaluated in 64-bit and rounded once."""
+
+    def __init__(self, spec, compute_dtype):
+        super().__init__(spec, compute_dtype)
+        layout = str(self.args.get("layout", "half"))
+        if layout not in ("half", "interleaved"):
+            raise ValueError(f"unknown pair layout {layout!r}; known: half, interleaved")
+        self.interleaved = layout == "interleaved"
+
+    def _frequencies(self):
+        exponents = torch.arange(0, self.head_dim, 2, dtype=torch.float64) / self.head_dim
+        return (self.theta ** -exponents).to(torch.float32)
+
+    def rotate_and_store(self, qkv, ctx, view, num_heads, num_kv_heads, head_dim, write_kv):
+        raise NotImplementedError("this encoding is applied by the mixer's own kernels")
+
+
 register_part("position", "rope_half", RotateHalfRope)
+register_part("position", "rope_pairs", PairedRope)

@@ -291,3 +291,100 @@ class FakeOps:
                 o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * out_scale
                 out[start + r] = o.reshape(-1).to(q.dtype)
         return out
+
+    # ---- 32-bit stream between layer norms, latent attention
+    def embedding_rows32(self, ids, table):
+        return table[ids.long()].float()
+
+    @staticmethod
+    def _layer_norm(v, pair, eps):
+        mean = v.mean(-1, keepdim=True)
+        centred = v - mean
+        return centred * torch.rsqrt((centred * centred).mean(-1, keepdim=True) + eps) * pair[0] + pair[1]
+
+    def layer_norm_step(self, x, eps, *, delta=None, delta_norm=None, offset=None, norm=None, out_dtype=None):
+        if delta is not None:
+            x += self._layer_norm(delta, delta_norm, eps)
+        if offset is not None:
+            x += offset
+        return None if norm is None else self._layer_norm(x, norm, eps).to(out_dtype or torch.float32)
+
+    def add_rows(self, x, vector):
+        x += vector
+        return x
+
+    def clamped_gate(self, gate_up, block, limit, slope):
+        inner = gate_up.shape[1] // 2
+        blocks = gate_up.float().view(gate_up.shape[0], inner // block, 2, block)
+        gate, up = blocks[:, :, 0].reshape(-1, inner), blocks[:, :, 1].reshape(-1, inner)
+        gate, up = gate.clamp(max=limit), up.clamp(-limit, limit)
+        return (gate * torch.sigmoid(slope * gate) * (up + 1.0)).to(gate_up.dtype)
+
+    def linear_clamped_gate(self, x, weight, block, limit, slope):
+        return self.clamped_gate(self.linear(x, weight), block, limit, slope)
+
+    def scale_(self, x, factor):
+        x *= factor
+        return x
+
+    @staticmethod
+    def _turn(vector, positions, frequencies, interleaved):
+        """vector [rows, ..., n]: the first 2 * len(frequencies) entries turned by the rows' positions."""
+        pairs = frequencies.shape[0]
+        out = vector.clone()
+        angle = positions.float()[:, None] * frequencies[None, :]
+        shape = (vector.shape[0],) + (1,) * (vector.dim() - 2) + (pairs,)
+        cos, sin = torch.cos(angle).view(shape), torch.sin(angle).view(shape)
+        first = torch.arange(pairs) * 2 if interleaved else torch.arange(pairs)
+        second = first + 1 if interleaved else first + pairs
+        u, v = vector[..., first], vector[..., second]
+        out[..., first] = u * cos - v * sin
+        out[..., second] = v * cos + u * sin
+        return out
+
+    def latent_prepare(self, down, q_at, q_rank, c_at, rank, rot, q_weight, c_weight, eps, positions, frequencies,
+                       interleaved, slots, pool, write=True):
+        def normed(t, weight):
+            return t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * weight
+
+        q_latent = normed(down[:, q_at:q_at + q_rank], q_weight).to(pool.dtype)
+        if write:
+            latent = normed(down[:, c_at:c_at + rank], c_weight)
+            turned = self._turn(down[:, c_at + rank:c_at + rank + rot], positions, frequencies, interleaved)
+            rows, page_size = torch.cat([latent, turned], dim=1).to(pool.dtype), pool.shape[2]
+            for t in range(down.shape[0]):
+                page, offset = divmod(int(slots[t]), page_size)
+                pool[page, 0, offset, :] = rows[t]
+        return q_latent
+
+    def absorb_queries(self, q, weight, heads, dim, rot, rank, positions, frequencies, interleaved):
+        q = q.view(-1, heads, dim + rot)
+        plain = torch.einsum("rhd,hdc->rhc", q[..., :dim], weight.float().view(heads, dim, rank))
+        turned = self._turn(q[..., dim:], positions, frequencies, interleaved)
+        return torch.cat([plain, turned], dim=-1).reshape(q.shape[0], -1).to(weight.dtype)
+
+    def latent_values(self, mixed, weight, heads, vdim, rank, gate, gate_per_head):
+        out = torch.einsum("rhc,hvc->rhv", mixed.view(-1, heads, rank), weight.float().view(heads, vdim, rank))
+        gate = torch.sigmoid(gate.float())
+        out = out * (gate[:, :, None] if gate_per_head else gate.view(-1, heads, vdim))
+        return out.reshape(mixed.shape[0], -1).to(weight.dtype)
+
+    def latent_attention(self, q, pool, batch, heads, rank, rot, scale, window, sink):
+        page_size = pool.shape[2]
+        out = torch.empty((q.shape[0], heads * rank), dtype=torch.float32)
+        q3 = q.float().view(-1, heads, rank + rot)
+        for seg in range(batch.num_segments):
+            start, length, pos0 = int(batch.seg_q_start[seg]), int(batch.seg_q_len[seg]), int(batch.seg_pos0[seg])
+            table = batch.block_table[int(batch.seg_slot[seg])]
+            for r in range(length):
+                p = pos0 + r
+                keys = torch.arange(max(0, p - window + 1) if window else 0, p + 1)
+                pages = table[(keys // page_size).long()].long()
+                assert (pages >= 0).all(), "attention reads a page the request does not hold"
+                rows = pool[pages, 0, (keys % page_size).long(), :].float()
+                scores = torch.einsum("hd,kd->hk", q3[start + r], rows) * scale
+                if sink is not None:
+                    scores = torch.cat([scores, sink[:, None]], dim=1)
+                weights = torch.softmax(scores, dim=-1)[:, :len(keys)]
+                out[start + r] = (weights @ rows[:, :rank]).reshape(-1)
+        return out
