@@ -85,6 +85,104 @@ layer_norm_step_kernel(float* x, const float* delta, const float* __restrict__ d
     out[base + d] = from_float<T>(fmaf((staged[d] - mean) * rstd, w[d], b[d]));
 }
 
+// The same with one warp per row and the row in registers (width a multiple of 4, at most CH * 128):
+// no barriers, 16-byte accesses.  Lane l holds the float4 pieces l, l + 32, ..
+__device__ __forceinline__ void store4(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+__device__ __forceinline__ void store4(bf16* dst, float4 v) {
+  uint2 packed;
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  packed.x = *reinterpret_cast<uint32_t*>(&lo);
+  packed.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+template <int CH>
+__device__ __forceinline__ void warp_row_statistics(const float4 (&v)[CH], int pieces, int lane, int width, float eps,
+                                                    float* mean_out, float* rstd_out) {
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < CH; ++j)
+    if (lane + 32 * j < pieces) sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+  const float mean = warp_sum(sum) / (float)width;
+  float sq = 0.f;
+#pragma unroll
+  for (int j = 0; j < CH; ++j)
+    if (lane + 32 * j < pieces) {
+      const float a = v[j].x - mean, b = v[j].y - mean, c = v[j].z - mean, d = v[j].w - mean;
+      sq += fmaf(a, a, b * b) + fmaf(c, c, d * d);
+    }
+  *mean_out = mean;
+  *rstd_out = 1.f / sqrtf(warp_sum(sq) / (float)width + eps);
+}
+
+__device__ __forceinline__ float4 normalised(float4 v, float mean, float rstd, float4 w, float4 b) {
+  return make_float4(fmaf((v.x - mean) * rstd, w.x, b.x), fmaf((v.y - mean) * rstd, w.y, b.y),
+                     fmaf((v.z - mean) * rstd, w.z, b.z), fmaf((v.w - mean) * rstd, w.w, b.w));
+}
+
+template <typename T, int CH>
+__global__ void __launch_bounds__(128)
+layer_norm_step_warp_kernel(float* x, const float* delta, const float* __restrict__ dw, const float* __restrict__ db,
+                            const float* __restrict__ offset, const float* __restrict__ w, const float* __restrict__ b,
+                            T* __restrict__ out, int rows, int width, float eps) {
+  pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int pieces = width >> 2;
+  pdl_wait();
+  if (row >= rows) return;
+  const size_t base = (size_t)row * width;
+  const float4* x4 = reinterpret_cast<const float4*>(x + base);
+  float4 v[CH];
+  float mean, rstd;
+  if (delta != nullptr) {
+    const float4* d4 = reinterpret_cast<const float4*>(delta + base);
+#pragma unroll
+    for (int j = 0; j < CH; ++j)
+      if (lane + 32 * j < pieces) v[j] = __ldcg(d4 + lane + 32 * j);
+    warp_row_statistics<CH>(v, pieces, lane, width, eps, &mean, &rstd);
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+      const int c = lane + 32 * j;
+      if (c < pieces) {
+        const float4 add = normalised(v[j], mean, rstd, reinterpret_cast<const float4*>(dw)[c],
+                                      reinterpret_cast<const float4*>(db)[c]);
+        float4 now = __ldcg(x4 + c);
+        now.x += add.x; now.y += add.y; now.z += add.z; now.w += add.w;
+        if (offset != nullptr) {
+          const float4 o = reinterpret_cast<const float4*>(offset)[c];
+          now.x += o.x; now.y += o.y; now.z += o.z; now.w += o.w;
+        }
+        v[j] = now;
+        store4(x + base + 4 * c, now);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+      const int c = lane + 32 * j;
+      if (c < pieces) {
+        float4 now = __ldcg(x4 + c);
+        if (offset != nullptr) {
+          const float4 o = reinterpret_cast<const float4*>(offset)[c];
+          now.x += o.x; now.y += o.y; now.z += o.z; now.w += o.w;
+          store4(x + base + 4 * c, now);
+        }
+        v[j] = now;
+      }
+    }
+  }
+  if (out == nullptr) return;
+  warp_row_statistics<CH>(v, pieces, lane, width, eps, &mean, &rstd);
+#pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    const int c = lane + 32 * j;
+    if (c < pieces)
+      store4(out + base + 4 * c, normalised(v[j], mean, rstd, reinterpret_cast<const float4*>(w)[c],
+                                            reinterpret_cast<const float4*>(b)[c]));
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 clamped_gate_kernel(const T* x, T* __restrict__ out, long long rows, int inner, int block, float limit, float slope) {
@@ -139,6 +237,27 @@ MLR_EXPORT int mlr_layer_norm_step(float* x, const float* delta, const float* dw
     return MLR_BAD_SIZE;
   const size_t shared = sizeof(float) * ((size_t)width + 32);
   if (shared > 200 * 1024) return MLR_TOO_LARGE;
+  auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (width % 4 == 0 && width <= 2048 && aligned(x) && aligned(delta) && aligned(dw) && aligned(db) && aligned(offset) &&
+      aligned(w) && aligned(b) && aligned(out)) {
+    // the row fits a warp's registers
+    auto launch_warp = [&](auto kernel, auto* typed_out) -> int {
+      launch_kernel(kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, x, delta, dw, db, offset, w, b, typed_out, rows,
+                    width, eps);
+      return launch_status();
+    };
+    if (out_dtype == MLR_F32) {
+      if (width <= 512) return launch_warp(layer_norm_step_warp_kernel<float, 4>, (float*)out);
+      if (width <= 1024) return launch_warp(layer_norm_step_warp_kernel<float, 8>, (float*)out);
+      return launch_warp(layer_norm_step_warp_kernel<float, 16>, (float*)out);
+    }
+    if (out_dtype == MLR_BF16) {
+      if (width <= 512) return launch_warp(layer_norm_step_warp_kernel<bf16, 4>, (bf16*)out);
+      if (width <= 1024) return launch_warp(layer_norm_step_warp_kernel<bf16, 8>, (bf16*)out);
+      return launch_warp(layer_norm_step_warp_kernel<bf16, 16>, (bf16*)out);
+    }
+    return MLR_BAD_DTYPE;
+  }
   auto launch = [&](auto kernel, auto* typed_out) -> int {
     if (shared > 48 * 1024) {
       cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);

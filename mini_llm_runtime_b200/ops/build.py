@@ -47,6 +47,7 @@ LIBRARIES: dict[str, tuple[str, ...]] = {
     "attention_diff_mma": (),
     "stream32": (),
     "attention_latent": (),
+    "attention_latent_mma": (),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -1118,6 +1118,14 @@ class CudaOps:
                 raise KernelError("gate must be a float32 view [rows, heads] or [rows, heads * n]")
             gate_ptr, gate_row = _ptr(gate), ctypes.c_longlong(gate.stride(0))
         pairs = 0 if frequencies is None else frequencies.shape[0]
+        if (self.use_tensor_cores and weight.dtype == torch.bfloat16 and n % 8 == 0 and k % 8 == 0 and x.stride(0) % 4 == 0
+                and x_head % 4 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
+            _check(build.load_library("attention_latent_mma").mlr_head_linear_mma(
+                _ptr(x), ctypes.c_longlong(x.stride(0)), x_head, _ptr(weight), _ptr(out), ctypes.c_longlong(out.stride(0)),
+                out_head, rows, heads, n, k, int(kn), mode, tail, pairs, int(bool(interleaved)), _ptr(positions),
+                _ptr(frequencies), gate_ptr, gate_row, int(bool(gate_per_head)), _code(out.dtype), _stream()),
+                "head_linear (tensor cores)")
+            return out
         _check(build.load_library("attention_latent").mlr_head_linear(
             _ptr(x), ctypes.c_longlong(x.stride(0)), x_head, _ptr(weight), _ptr(out), ctypes.c_longlong(out.stride(0)),
             out_head, rows, heads, n, k, int(kn), mode, tail, pairs, int(bool(interleaved)), _ptr(positions),
@@ -1172,19 +1180,50 @@ class CudaOps:
         tail = (heads, rank, rot, pool.shape[2], int(window or 0), ctypes.c_float(scale), _ptr(sink), _code(q.dtype),
                 _stream())
         tiles = batch.counts["tiles"]
-        if self.use_latent_decode_kernel and batch.num_decode > 0:
+        on_tensor_cores = self.use_mma_attention and q.dtype == torch.bfloat16 and self._latent_mma_fits(rank, rot)
+        if self.use_latent_decode_kernel and batch.num_decode > 0 and on_tensor_cores:
+            # decoded rows on the tensor cores: a row's heads are the rows of the products, its keys cut into
+            # chunks so that the step's CTAs fill the device about twice
+            listed = None if batch.num_decode == batch.num_segments else batch.plan["decode_seg"]
+            longest = min(batch.max_kv_len, window + 31) if window else batch.max_kv_len
+            key_tiles = -(-longest // 32) + 1
+            groups = batch.num_decode * -(-(-(-heads // 16)) // 2)
+            chunks = max(1, min(key_tiles // 2, 2 * self.sm_count(q.device) // groups))
+            partial = None
+            if chunks > 1:
+                partial = torch.empty(batch.num_decode * chunks * heads * (rank + 2), dtype=torch.float32, device=q.device)
+            _check(build.load_library("attention_latent_mma").mlr_latent_attention_mma_decode(
+                _ptr(q), _ptr(pool), _ptr(out), _ptr(listed), batch.num_decode, chunks, _ptr(partial),
+                _ptr(batch.seg_q_start), _ptr(batch.seg_pos0), _ptr(batch.block_table), _ptr(batch.seg_slot),
+                batch.block_table.shape[1], heads, rank, rot, pool.shape[2], int(window or 0), ctypes.c_float(scale),
+                _ptr(sink), _stream()), "latent attention (decode, tensor cores)")
+            tiles -= batch.num_decode
+        elif self.use_latent_decode_kernel and batch.num_decode > 0:
             listed = None if batch.num_decode == batch.num_segments else batch.plan["decode_seg"]
             _check(lib.mlr_latent_attention_decode(
                 _ptr(q), _ptr(pool), _ptr(out), _ptr(listed), batch.num_decode, _ptr(batch.seg_q_start),
                 _ptr(batch.seg_pos0), _ptr(batch.block_table), _ptr(batch.seg_slot), batch.block_table.shape[1], *tail),
                 "latent attention (decode)")
             tiles -= batch.num_decode       # the one-row segments' tiles are the last of the list
-        if tiles > 0:
+        if tiles > 0 and on_tensor_cores:
+            # prompt portions on the tensor cores
+            _check(build.load_library("attention_latent_mma").mlr_latent_attention_mma(
+                _ptr(q), _ptr(pool), _ptr(out), _ptr(batch.plan["tile_seg"]), _ptr(batch.plan["tile_row0"]),
+                _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0), _ptr(batch.block_table),
+                _ptr(batch.seg_slot), batch.block_table.shape[1], tiles, heads, rank, rot, pool.shape[2],
+                int(window or 0), ctypes.c_float(scale), _ptr(sink), _stream()), "latent attention (tensor cores)")
+        elif tiles > 0:
             _check(lib.mlr_latent_attention(
                 _ptr(q), _ptr(pool), _ptr(out), _ptr(batch.plan["tile_seg"]), _ptr(batch.plan["tile_row0"]),
                 _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_pos0), _ptr(batch.block_table),
                 _ptr(batch.seg_slot), batch.block_table.shape[1], tiles, *tail), "latent attention")
         return out
+
+    def _latent_mma_fits(self, rank: int, rot: int) -> bool:
+        cache = self.__dict__.setdefault("_latent_fits", {})
+        if (rank, rot) not in cache:
+            cache[(rank, rot)] = bool(build.load_library("attention_latent_mma").mlr_latent_attention_mma_fits(rank, rot))
+        return cache[(rank, rot)]
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch.Tensor,

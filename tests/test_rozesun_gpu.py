@@ -293,3 +293,78 @@ def test_command_line_and_replay_program_with_a_model_folder(tmp_path):
     want = plain.forward(rs.MIXED, tensors, prompt)
     rs.assert_logits_close(torch.cat([first, second[:1]]), want[[0, 3, 10]], F32)
     rs.assert_logits_close(second[1:], plain.forward(rs.MIXED, tensors, other)[29:], F32)
+
+
+def _attention_case(lengths, positions, heads, rank, rot, page=16, seed=0):
+    """A ragged batch over a paged cache of random rows, as the attention kernels take it."""
+    import numpy as np
+
+    from mini_llm_runtime_b200.ops.cuda_ops import AttentionBatch, plan_attention
+
+    generator = torch.Generator().manual_seed(seed)
+    lengths, positions = np.asarray(lengths, dtype=np.int32), np.asarray(positions, dtype=np.int32)
+    starts = np.zeros_like(lengths)
+    np.cumsum(lengths[:-1], out=starts[1:])
+    per_request = -(-int((positions + lengths).max()) // page)
+    order = torch.randperm(len(lengths) * per_request, generator=generator).to(torch.int32)      # pages in any order
+    table = order.view(len(lengths), per_request).to(DEVICE)
+    pool = torch.randn(len(lengths) * per_request, 1, page, rank + rot, generator=generator).to(torch.bfloat16).to(DEVICE)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(DEVICE)      # noqa: E731
+    arrays, counts = plan_attention(lengths, positions)
+    batch = AttentionBatch(dev(starts), dev(lengths), dev(positions), dev(np.arange(len(lengths))), table, len(lengths),
+                           int(lengths.max()), int((positions + lengths).max()), {n: dev(v) for n, v in arrays.items()}, counts)
+    q = (torch.randn(int(lengths.sum()), heads * (rank + rot), generator=generator) * 0.3).to(torch.bfloat16).to(DEVICE)
+    return q, pool, batch
+
+
+@pytest.mark.parametrize("heads,rank,rot,window,sink", [(3, 40, 8, 0, False), (2, 96, 32, 37, True), (18, 64, 16, 100, True),
+                                                         (16, 512, 64, 0, False), (1, 24, 8, 9, True)])
+def test_tensor_core_attention_against_the_float32_kernel(heads, rank, rot, window, sink):
+    """Prompt portions beside decoded rows (some in several key chunks) on the tensor-core kernels
+    against the float32 kernels on the same bfloat16 rows."""
+    from mini_llm_runtime_b200 import ops
+    k = ops.current()
+    q, pool, batch = _attention_case([70, 1, 33, 1, 1], [130, 299, 0, 40, 0], heads, rank, rot, seed=heads)
+    sinks = torch.linspace(-1.0, 2.0, heads).to(DEVICE) if sink else None
+    got = k.latent_attention(q, pool, batch, heads, rank, rot, 0.11, window, sinks)
+    k.use_mma_attention = False
+    try:
+        want = k.latent_attention(q, pool, batch, heads, rank, rot, 0.11, window, sinks)
+    finally:
+        k.use_mma_attention = True
+    assert float((got - want).abs().max()) < 2e-2 * float(want.abs().max())
+    assert float((got - want).pow(2).mean().sqrt()) < 3e-3 * float(want.pow(2).mean().sqrt())
+
+
+@pytest.mark.parametrize("rows", [1, 9, 150])
+def test_per_head_products_against_the_formula(rows):
+    from mini_llm_runtime_b200 import ops
+    k = ops.current()
+    generator = torch.Generator().manual_seed(rows)
+    heads, dim, rot, rank, vdim = 3, 24, 8, 40, 16
+    q = torch.randn(rows, heads * (dim + rot), generator=generator)
+    w_uk = (torch.randn(heads * dim, rank, generator=generator) * 0.2).to(torch.bfloat16)
+    positions = torch.arange(5, 5 + rows, dtype=torch.int32)
+    frequencies = torch.tensor([1.0, 0.3, 0.02])        # three pairs: the last two of the eight entries pass unchanged
+    for interleaved in (False, True):
+        got = k.absorb_queries(q.to(DEVICE), w_uk.to(DEVICE), heads, dim, rot, rank, positions.to(DEVICE),
+                               frequencies.to(DEVICE), interleaved).float().cpu().view(rows, heads, rank + rot)
+        q3 = q.double().view(rows, heads, dim + rot)
+        plain_part = torch.einsum("rhd,hdc->rhc", q3[..., :dim], w_uk.double().view(heads, dim, rank))
+        turned = plain.rotate(q3[..., dim:], positions, 1.0, 6, interleaved)      # base 1: frequencies set below
+        for i, f in enumerate(frequencies.tolist()):                              # the oracle's rotation with these angles
+            a, b = (2 * i, 2 * i + 1) if interleaved else (i, i + 3)
+            angle = positions.double() * f
+            u, v = q3[..., dim + a], q3[..., dim + b]
+            turned[..., a] = u * torch.cos(angle)[:, None] - v * torch.sin(angle)[:, None]
+            turned[..., b] = v * torch.cos(angle)[:, None] + u * torch.sin(angle)[:, None]
+        want = torch.cat([plain_part, turned], dim=-1)
+        assert float((got - want).abs().max()) < 2e-2 * float(want.abs().max())
+    mixed = torch.randn(rows, heads * rank, generator=generator)
+    w_uv = (torch.randn(heads * vdim, rank, generator=generator) * 0.2).to(torch.bfloat16)
+    for per_head in (False, True):
+        gate = torch.randn(rows, heads if per_head else heads * vdim, generator=generator)
+        got = k.latent_values(mixed.to(DEVICE), w_uv.to(DEVICE), heads, vdim, rank, gate.to(DEVICE), per_head).float().cpu()
+        want = torch.einsum("rhc,hvc->rhv", mixed.double().view(rows, heads, rank), w_uv.double().view(heads, vdim, rank))
+        want = want * (torch.sigmoid(gate.double())[:, :, None] if per_head else torch.sigmoid(gate.double()).view(rows, heads, vdim))
+        assert float((got.view(rows, heads, vdim) - want).abs().max()) < 2e-2 * float(want.abs().max())
