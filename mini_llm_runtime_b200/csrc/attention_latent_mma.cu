@@ -23,7 +23,6 @@
 namespace mlr {
 
 constexpr int LM_TOKENS = 16;      // tokens per CTA
-constexpr int LM_HEADS = 2;        // most warp groups per CTA: heads of a prompt tile, or blocks of 16 heads of a decoded row
 constexpr int LM_SPLIT = 4;        // warps per head
 constexpr int LM_KEYS = 32;        // keys per tile, 8 per warp
 constexpr int LM_MAX_NT = 16;      // value column blocks of 8 per warp: rank <= 4 * 16 * 8
@@ -38,11 +37,13 @@ struct LatentMmaArgs {
   float* partial;            // decoded rows in several chunks: [item][chunk][head][rank + 2]
 };
 
+// Keys key0 .. key0 + 31 into a tile: each warp takes rows in turn, looks the row's page up once and its
+// lanes copy the row's 16-byte pieces.  Keys outside [key_lo, key_hi] or on pages the request does not
+// hold become zeros.
 __device__ __forceinline__ void load_key_tile(bf16* tile, int stride, const bf16* pool, const int* __restrict__ table,
                                               int key0, int key_lo, int key_hi, int page_size, int dk) {
-  const int chunks = dk >> 3;
-  for (int item = threadIdx.x; item < LM_KEYS * chunks; item += blockDim.x) {
-    const int r = item / chunks, c = item - r * chunks;
+  const int chunks = dk >> 3, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int r = threadIdx.x >> 5; r < LM_KEYS; r += warps) {
     const int key = key0 + r;
     bool valid = key >= key_lo && key <= key_hi;
     const bf16* src = pool;
@@ -50,9 +51,9 @@ __device__ __forceinline__ void load_key_tile(bf16* tile, int stride, const bf16
       const int logical = key / page_size;
       const int page = table[logical];
       valid = page >= 0;
-      if (valid) src = pool + ((size_t)page * page_size + (key - logical * page_size)) * dk + c * 8;
+      if (valid) src = pool + ((size_t)page * page_size + (key - logical * page_size)) * dk;
     }
-    cp_async_16(tile + r * stride + c * 8, src, valid);
+    for (int c = lane; c < chunks; c += 32) cp_async_16(tile + r * stride + c * 8, valid ? src + c * 8 : pool, valid);
   }
 }
 
@@ -130,20 +131,24 @@ latent_mma_kernel(const bf16* q, const bf16* pool, float* __restrict__ out, cons
     cp_async_commit();
     const bf16* k_tile = k_tiles + buffer * LM_KEYS * S;
 
-    // scores of this warp's 8 keys
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    // scores of this warp's 8 keys; two chains of sums, over the even and the odd 16-channel steps
+    float s[4] = {0.f, 0.f, 0.f, 0.f}, s_odd[4] = {0.f, 0.f, 0.f, 0.f};
+    const bf16* q_lane = q_mine + ((lane & 7) + ((lane >> 3) & 1) * 8) * S + (lane >> 4) * 8;
+    const bf16* k_lane = k_tile + (split * 8 + (lane & 7)) * S;
+#pragma unroll 2
     for (int ks = 0; ks < DK / 16; ks += 2) {
-      uint32_t b[4], a[4];
+      uint32_t b[4], a[4], a_next[4];
       // keys split*8 .. +7, channel chunks 2*ks .. 2*ks+3 (the last two may lie past DK when DK/16 is odd)
       const int chunk = min(ks * 2 + (lane >> 3), chunks - 1);
-      ldmatrix_x4(b, k_tile + (split * 8 + (lane & 7)) * S + chunk * 8);
-      ldmatrix_x4(a, q_mine + ((lane & 7) + ((lane >> 3) & 1) * 8) * S + (ks * 2 + (lane >> 4)) * 8);
+      ldmatrix_x4(b, k_lane + chunk * 8);
+      ldmatrix_x4(a, q_lane + ks * 16);
+      const bool pair = ks + 1 < DK / 16;
+      if (pair) ldmatrix_x4(a_next, q_lane + ks * 16 + 16);
       mma_bf16(s, a, b[0], b[1]);
-      if (ks + 1 < DK / 16) {
-        ldmatrix_x4(a, q_mine + ((lane & 7) + ((lane >> 3) & 1) * 8) * S + (ks * 2 + 2 + (lane >> 4)) * 8);
-        mma_bf16(s, a, b[2], b[3]);
-      }
+      if (pair) mma_bf16(s_odd, a_next, b[2], b[3]);
     }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[e] += s_odd[e];
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -271,21 +276,25 @@ latent_merge_kernel(const float* partial, float* __restrict__ out, const int* __
   const int seg = decode_seg != nullptr ? decode_seg[item] : item;
   const float* mine = partial + ((size_t)item * chunks * heads + head) * (rank + 2);
   const size_t step = (size_t)heads * (rank + 2);
-  float top = sink != nullptr ? sink[head] * 1.4426950408889634f : -INFINITY;
-  for (int c = 0; c < chunks; ++c) top = fmaxf(top, mine[c * step + rank]);
-  float total = sink != nullptr ? exp2f(sink[head] * 1.4426950408889634f - top) : 0.f;
+  // lane c holds chunk c's maximum and denominator (at most 32 chunks), so that all of them are asked for at once
+  const float sink_log2 = sink != nullptr ? sink[head] * 1.4426950408889634f : -INFINITY;
+  const float my_max = lane < chunks ? __ldcg(mine + lane * step + rank) : -INFINITY;
+  const float my_sum = lane < chunks ? __ldcg(mine + lane * step + rank + 1) : 0.f;
+  const float top = fmaxf(warp_max(my_max), sink_log2);
+  const float my_factor = my_max == -INFINITY ? 0.f : exp2f(my_max - top);
+  float total = warp_sum(my_sum * my_factor);
+  if (sink != nullptr) total += exp2f(sink_log2 - top);
   float sums[LM_SPLIT * LM_MAX_NT * 8 / 32];
 #pragma unroll
   for (int j = 0; j < LM_SPLIT * LM_MAX_NT * 8 / 32; ++j) sums[j] = 0.f;
+#pragma unroll 4
   for (int c = 0; c < chunks; ++c) {
     const float* theirs = mine + c * step;
-    if (theirs[rank] == -INFINITY) continue;
-    const float f = exp2f(theirs[rank] - top);
-    total = fmaf(theirs[rank + 1], f, total);
+    const float f = __shfl_sync(0xffffffffu, my_factor, c);
 #pragma unroll
     for (int j = 0; j < LM_SPLIT * LM_MAX_NT * 8 / 32; ++j) {
       const int d = lane + 32 * j;
-      if (d < rank) sums[j] = fmaf(theirs[d], f, sums[j]);
+      if (d < rank) sums[j] = fmaf(__ldcg(theirs + d), f, sums[j]);
     }
   }
   const float inv = 1.f / total;
@@ -312,24 +321,30 @@ struct HeadMmaArgs {
   const float* gate; long long gate_row; int gate_per_head;
 };
 
-constexpr int HM_ROWS = 64, HM_COLS = 64, HM_K = 32;
+constexpr int HM_COLS = 64;
 
-template <typename TO>
+// FEW: at most 16 rows per CTA (decode steps): the four warps share the rows and take 16 columns each,
+// and k advances 128 at a time, so that a product over a latent of 512 is four rounds of loads instead
+// of sixteen.
+template <typename TO, bool FEW>
 __global__ void __launch_bounds__(128)
 head_linear_mma_kernel(const bf16* __restrict__ w, TO* __restrict__ y, HeadMmaArgs p) {
   pdl_trigger();
-  __shared__ __align__(16) bf16 a_tile[HM_ROWS * (HM_K + 8)];
-  __shared__ __align__(16) bf16 b_tile[HM_COLS * (HM_K + 8) > HM_K * (HM_COLS + 8) ? HM_COLS * (HM_K + 8) : HM_K * (HM_COLS + 8)];
+  constexpr int HM_ROWS = FEW ? 16 : 64, HM_K = FEW ? 128 : 32;
   constexpr int AS = HM_K + 8, BS_NK = HM_K + 8, BS_KN = HM_COLS + 8;
+  __shared__ __align__(16) bf16 a_tile[HM_ROWS * AS];
+  __shared__ __align__(16) bf16 b_tile[HM_COLS * BS_NK > HM_K * BS_KN ? HM_COLS * BS_NK : HM_K * BS_KN];
   const int head = blockIdx.z, row0 = blockIdx.y * HM_ROWS, n0 = blockIdx.x * HM_COLS;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warp_row = FEW ? 0 : warp * 16, warp_col = FEW ? warp * 16 : 0;
+  constexpr int NT = FEW ? 2 : HM_COLS / 8;        // column blocks of 8 per warp
   const bf16* wh = w + (size_t)head * p.N * p.K;
-  float acc[HM_COLS / 8][4];
+  float acc[NT][4];
 #pragma unroll
-  for (int j = 0; j < HM_COLS / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
   pdl_wait();
   for (int k0 = 0; k0 < p.K; k0 += HM_K) {
-    // x: 64 rows x 32 floats as float4 pieces
+    // x: rows x HM_K floats as float4 pieces, rounded to bfloat16
     for (int item = threadIdx.x; item < HM_ROWS * HM_K / 4; item += 128) {
       const int r = item / (HM_K / 4), c = item - r * (HM_K / 4);
       const int row = row0 + r, k = k0 + 4 * c;
@@ -362,14 +377,15 @@ head_linear_mma_kernel(const bf16* __restrict__ w, TO* __restrict__ y, HeadMmaAr
 #pragma unroll
     for (int kk = 0; kk < HM_K / 16; ++kk) {
       uint32_t a[4];
-      ldmatrix_x4(a, a_tile + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * AS + (kk * 2 + (lane >> 4)) * 8);
+      ldmatrix_x4(a, a_tile + (warp_row + (lane & 7) + ((lane >> 3) & 1) * 8) * AS + (kk * 2 + (lane >> 4)) * 8);
 #pragma unroll
-      for (int jp = 0; jp < HM_COLS / 16; ++jp) {
+      for (int jp = 0; jp < NT / 2; ++jp) {
         uint32_t b[4];
+        const int col = warp_col + jp * 16;
         if (p.kn)
-          ldmatrix_x4_trans(b, b_tile + (kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * BS_KN + (jp * 2 + (lane >> 4)) * 8);
+          ldmatrix_x4_trans(b, b_tile + (kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * BS_KN + col + (lane >> 4) * 8);
         else
-          ldmatrix_x4(b, b_tile + (jp * 16 + (lane & 7) + ((lane >> 4) << 3)) * BS_NK + (kk * 2 + ((lane >> 3) & 1)) * 8);
+          ldmatrix_x4(b, b_tile + (col + (lane & 7) + ((lane >> 4) << 3)) * BS_NK + (kk * 2 + ((lane >> 3) & 1)) * 8);
         mma_bf16(acc[2 * jp], a, b[0], b[1]);
         mma_bf16(acc[2 * jp + 1], a, b[2], b[3]);
       }
@@ -378,13 +394,13 @@ head_linear_mma_kernel(const bf16* __restrict__ w, TO* __restrict__ y, HeadMmaAr
   }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    const int row = row0 + warp * 16 + (lane >> 2) + 8 * i;
+    const int row = row0 + warp_row + (lane >> 2) + 8 * i;
     if (row >= p.rows) continue;
 #pragma unroll
-    for (int j = 0; j < HM_COLS / 8; ++j) {
+    for (int j = 0; j < NT; ++j) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const int n = n0 + j * 8 + (lane & 3) * 2 + e;
+        const int n = n0 + warp_col + j * 8 + (lane & 3) * 2 + e;
         if (n >= p.N) continue;
         float v = acc[j][2 * i + e];
         if (p.mode == 2) {
@@ -433,7 +449,7 @@ static size_t latent_mma_shared(int groups, int dk) {
 MLR_EXPORT int mlr_latent_attention_mma_fits(int rank, int rot) {
   const int dk = rank + rot;
   return rank > 0 && rank % 8 == 0 && rank <= LM_SPLIT * LM_MAX_NT * 8 && rot >= 8 && dk % 16 == 0 &&
-         latent_mma_shared(LM_HEADS, dk) <= 200 * 1024;
+         latent_mma_shared(2, dk) <= 200 * 1024;
 }
 
 template <int G, bool DECODE>
@@ -478,8 +494,11 @@ MLR_EXPORT int mlr_latent_attention_mma(const void* q, const void* pool, float* 
   if (status != MLR_OK) return status;
   if (heads == 1)
     return latent_mma_launch<1, false>(q, pool, out, tile_seg, tile_row0, dim3(tiles, 1), args, stream);
-  return latent_mma_launch<LM_HEADS, false>(q, pool, out, tile_seg, tile_row0, dim3(tiles, (heads + LM_HEADS - 1) / LM_HEADS),
-                                            args, stream);
+  // four heads over one key tile where that many fit: the key tiles are fetched half as often and an SM
+  // holds sixteen warps instead of eight
+  if (heads > 2 && latent_mma_shared(4, rank + rot) <= 200 * 1024)
+    return latent_mma_launch<4, false>(q, pool, out, tile_seg, tile_row0, dim3(tiles, (heads + 3) / 4), args, stream);
+  return latent_mma_launch<2, false>(q, pool, out, tile_seg, tile_row0, dim3(tiles, (heads + 1) / 2), args, stream);
 }
 
 // Floats of scratch a decode call with `chunks` key chunks needs (0 for one chunk).
@@ -496,7 +515,7 @@ MLR_EXPORT int mlr_latent_attention_mma_decode(const void* q, const void* pool, 
                                                int table_width, int heads, int rank, int rot, int page_size, int window,
                                                float scale, const float* sink, cudaStream_t stream) {
   if (count == 0) return MLR_OK;
-  if (count < 0 || chunks < 1 || chunks > 65535 || (chunks > 1 && partial == nullptr)) return MLR_BAD_SIZE;
+  if (count < 0 || chunks < 1 || chunks > 32 || (chunks > 1 && partial == nullptr)) return MLR_BAD_SIZE;
   LatentMmaArgs args;
   int status = latent_mma_args(args, q, pool, out, seg_q_start, nullptr, seg_pos0, block_table, seg_slot, table_width,
                                heads, rank, rot, page_size, window, scale, sink);
@@ -507,8 +526,7 @@ MLR_EXPORT int mlr_latent_attention_mma_decode(const void* q, const void* pool, 
   if (blocks16 == 1)
     status = latent_mma_launch<1, true>(q, pool, out, nullptr, nullptr, dim3(count, 1, chunks), args, stream);
   else
-    status = latent_mma_launch<LM_HEADS, true>(q, pool, out, nullptr, nullptr,
-                                               dim3(count, (blocks16 + LM_HEADS - 1) / LM_HEADS, chunks), args, stream);
+    status = latent_mma_launch<2, true>(q, pool, out, nullptr, nullptr, dim3(count, (blocks16 + 1) / 2, chunks), args, stream);
   if (status != MLR_OK || chunks == 1) return status;
   const long long units = (long long)count * heads;
   launch_kernel(latent_merge_kernel, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, stream, (const float*)partial, out,
@@ -525,7 +543,7 @@ MLR_EXPORT int mlr_head_linear_mma(const float* x, long long x_row, int x_head, 
                                    long long gate_row, int gate_per_head, int y_dtype, cudaStream_t stream) {
   if (rows == 0) return MLR_OK;
   if (rows < 0 || heads <= 0 || N <= 0 || K <= 0 || tail < 0 || pairs < 0 || 2 * pairs > tail) return MLR_BAD_SIZE;
-  if (heads > 65535 || (rows + HM_ROWS - 1) / HM_ROWS > 65535) return MLR_TOO_LARGE;
+  if (heads > 65535 || (rows + 63) / 64 > 65535) return MLR_TOO_LARGE;
   if (N % 8 || K % 8 || x_row % 4 || x_head % 4 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return MLR_BAD_ALIGNMENT;
   if (mode == 1 && tail > 0 && pairs > 0 && (positions == nullptr || frequencies == nullptr)) return MLR_BAD_SIZE;
@@ -534,12 +552,16 @@ MLR_EXPORT int mlr_head_linear_mma(const float* x, long long x_row, int x_head, 
   p.x = x; p.x_row = x_row; p.x_head = x_head; p.y_row = y_row; p.y_head = y_head; p.rows = rows; p.heads = heads;
   p.N = N; p.K = K; p.kn = kn; p.mode = mode; p.tail = mode == 1 ? tail : 0; p.pairs = pairs; p.interleaved = interleaved;
   p.positions = positions; p.frequencies = frequencies; p.gate = gate; p.gate_row = gate_row; p.gate_per_head = gate_per_head;
-  const dim3 grid((N + HM_COLS - 1) / HM_COLS, (rows + HM_ROWS - 1) / HM_ROWS, heads);
-  if (y_dtype == MLR_BF16)
-    launch_kernel(head_linear_mma_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)w, (bf16*)y, p);
-  else if (y_dtype == MLR_F32)
-    launch_kernel(head_linear_mma_kernel<float>, grid, dim3(128), 0, stream, (const bf16*)w, (float*)y, p);
-  else
+  const bool few = rows <= 16;
+  const dim3 grid((N + HM_COLS - 1) / HM_COLS, few ? 1 : (rows + 63) / 64, heads);
+  if (y_dtype == MLR_BF16) {
+    if (few) launch_kernel(head_linear_mma_kernel<bf16, true>, grid, dim3(128), 0, stream, (const bf16*)w, (bf16*)y, p);
+    else launch_kernel(head_linear_mma_kernel<bf16, false>, grid, dim3(128), 0, stream, (const bf16*)w, (bf16*)y, p);
+  } else if (y_dtype == MLR_F32) {
+    if (few) launch_kernel(head_linear_mma_kernel<float, true>, grid, dim3(128), 0, stream, (const bf16*)w, (float*)y, p);
+    else launch_kernel(head_linear_mma_kernel<float, false>, grid, dim3(128), 0, stream, (const bf16*)w, (float*)y, p);
+  } else {
     return MLR_BAD_DTYPE;
+  }
   return launch_status();
 }

@@ -123,6 +123,15 @@ __device__ __forceinline__ float gate_times(int act, float gate, float up) {
   return __fdividef(gate * up, 1.f + e);
 }
 
+// The same with the clamped gate as act 2: g * sigmoid(slope * g) * (u + 1), g = min(gate, limit),
+// u = clamp(up, -limit, limit).
+__device__ __forceinline__ float gate_times(int act, float gate, float up, float limit, float slope) {
+  if (act != 2) return gate_times(act, gate, up);
+  const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+  const float e = __expf(fminf(-slope * g, 80.f));
+  return __fdividef(g * (u + 1.f), 1.f + e);
+}
+
 // One rotate-half pair: (x1, x2) turned by the angle whose sine and cosine are given.  Written with
 // explicit roundings so that every kernel that rotates gets the same bits.
 __device__ __forceinline__ void rotate_pair(float x1, float x2, float sine, float cosine, float* y1, float* y2) {

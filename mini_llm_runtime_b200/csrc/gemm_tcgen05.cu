@@ -129,7 +129,8 @@ struct GemmParams {
   const bf16* bias;
   void* out;
   int out_f32;
-  int gate_act;             // gated products: 0 silu(gate) * up, 1 gelu_tanh(gate) * up
+  int gate_act;             // gated products: 0 silu(gate) * up, 1 gelu_tanh(gate) * up, 2 the clamped gate
+  float gate_limit, gate_slope;   // of the clamped gate: min(gate, limit) * sigmoid(slope * .) * (clamp(up, +-limit) + 1)
   float* scratch;           // [tiles][splits][BN][128] partial tiles (splits > 1)
   int* counters;            // one per output tile, zero between launches
   int* error_word;
@@ -259,8 +260,8 @@ __device__ __forceinline__ void reduce_swapped_swiglu(const float* partials, int
     for (int j = 0; j < CB; ++j) {
       const int col = c + 8 * j, m = b_row0 + col;
       if (col >= BN || m >= p.M) continue;
-      const float v[4] = {gate_times(p.gate_act, gate[j].x, up[j].x), gate_times(p.gate_act, gate[j].y, up[j].y),
-                          gate_times(p.gate_act, gate[j].z, up[j].z), gate_times(p.gate_act, gate[j].w, up[j].w)};
+      const float v[4] = {gate_times(p.gate_act, gate[j].x, up[j].x, p.gate_limit, p.gate_slope), gate_times(p.gate_act, gate[j].y, up[j].y, p.gate_limit, p.gate_slope),
+                          gate_times(p.gate_act, gate[j].z, up[j].z, p.gate_limit, p.gate_slope), gate_times(p.gate_act, gate[j].w, up[j].w, p.gate_limit, p.gate_slope)};
       bf16* dst = (bf16*)p.out + (size_t)m * half + n0;
       if (wide) {
         __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
@@ -486,8 +487,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int c = 0; c < 16; c += 2) {
               __nv_bfloat162 pair = __floats2bfloat162_rn(
-                  gate_times(p.gate_act, __uint_as_float(g[q + c]), __uint_as_float(u[q + c])),
-                  gate_times(p.gate_act, __uint_as_float(g[q + c + 1]), __uint_as_float(u[q + c + 1])));
+                  gate_times(p.gate_act, __uint_as_float(g[q + c]), __uint_as_float(u[q + c]), p.gate_limit, p.gate_slope),
+                  gate_times(p.gate_act, __uint_as_float(g[q + c + 1]), __uint_as_float(u[q + c + 1]), p.gate_limit, p.gate_slope));
               packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
             }
             if ((half & 7) == 0 && n0 + 16 <= half) {
@@ -779,13 +780,15 @@ MLR_EXPORT long long mlr_gemm_tcgen05_plan(int M, int N, int K, int swiglu, int*
 
 // x [M,K], w [N,K], bias [N] or null, all bfloat16; out [M,N] bfloat16 (out_f32 = 0) or float32.
 // swiglu != 0: w holds blocks of 64 gate rows followed by the 64 up rows of the same outputs and the
-// result is act(gate) * up, act being silu (swiglu == 1) or the tanh form of gelu (swiglu == 2)
+// result is act(gate) * up, act being silu (swiglu == 1) or the tanh form of gelu (swiglu == 2), or
+// (swiglu == 3) the clamped gate g * sigmoid(gate_slope * g) * (u + 1) with g = min(gate, gate_limit) and
+// u = clamp(up, -gate_limit, gate_limit)
 // (N % 128 == 0, no bias) and out is silu(gate) * up, [M, N/2] bfloat16.
 // scratch: at least mlr_gemm_tcgen05_plan(...) bytes; counters: one zeroed int per tile;
 // error_word: host-visible int that receives a non-zero code if a wait inside the kernel runs out.
 MLR_EXPORT int mlr_gemm_tcgen05(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
-                                int out_f32, int swiglu, void* scratch, int* counters, int* error_word,
-                                cudaStream_t stream) {
+                                int out_f32, int swiglu, float gate_limit, float gate_slope, void* scratch, int* counters,
+                                int* error_word, cudaStream_t stream) {
   if (M == 0) return MLR_OK;
   if (M < 0 || N <= 0 || K <= 0) return MLR_BAD_SIZE;
   if (K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return MLR_BAD_ALIGNMENT;
@@ -799,7 +802,9 @@ MLR_EXPORT int mlr_gemm_tcgen05(const void* x, const void* w, const void* bias, 
   p.bias = (const bf16*)bias;
   p.out = out;
   p.out_f32 = out_f32;
-  p.gate_act = swiglu == 2 ? 1 : 0;
+  p.gate_act = swiglu >= 2 ? swiglu - 1 : 0;
+  p.gate_limit = gate_limit;
+  p.gate_slope = gate_slope;
   p.scratch = (float*)scratch;
   p.counters = counters;
   p.error_word = error_word;

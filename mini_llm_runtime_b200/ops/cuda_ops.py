@@ -550,7 +550,7 @@ class CudaOps:
                "linear (few rows)")
         return out
 
-    def _linear_tcgen05(self, x, weight, bias, out_dtype, swiglu=False):
+    def _linear_tcgen05(self, x, weight, bias, out_dtype, swiglu=False, gate=(0.0, 0.0)):
         M, K = x.shape
         N = weight.shape[0]
         lib = build.load_library("gemm_tcgen05")
@@ -562,7 +562,8 @@ class CudaOps:
             return None
         out = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
         _check(lib.mlr_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), M, N, K,
-                                    int(out_dtype == torch.float32), int(swiglu), _ptr(space["gemm_scratch"]),
+                                    int(out_dtype == torch.float32), int(swiglu), ctypes.c_float(gate[0]),
+                                    ctypes.c_float(gate[1]), _ptr(space["gemm_scratch"]),
                                     _ptr(space["gemm_counters"]), _ptr(space["error_word"]), _stream()),
                "linear (tcgen05)")
         return out
@@ -1062,6 +1063,17 @@ class CudaOps:
 
     def linear_clamped_gate(self, x: torch.Tensor, weight: torch.Tensor, block: int, limit: float, slope: float) -> torch.Tensor:
         """The clamped gate of (x Wg^T, x Wu^T) for ``weight`` [2*inner, K] of interleaved gate/up blocks."""
+        _need(x, "x", dims=2)
+        _need(weight, "weight", x.dtype, 2)
+        if x.shape[1] != weight.shape[1] or weight.shape[0] % (2 * block):
+            raise KernelError("linear_clamped_gate: shapes do not fit the interleaved gate/up layout")
+        if (self.use_tensor_cores and self.use_fused_swiglu and block == self.SWIGLU_BLOCK and x.dtype == torch.bfloat16
+                and x.shape[1] % 8 == 0 and x.shape[0] > 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
+                and not self._skinny_fits(x, weight)):
+            # many rows: the gate in the tensor-core product's epilogue
+            out = self._linear_tcgen05(x, weight, None, torch.bfloat16, swiglu=3, gate=(float(limit), float(slope)))
+            if out is not None:
+                return out
         return self.clamped_gate(self.linear(x, weight), block, limit, slope)
 
     def scale_(self, x: torch.Tensor, factor: float) -> torch.Tensor:
@@ -1188,7 +1200,8 @@ class CudaOps:
             longest = min(batch.max_kv_len, window + 31) if window else batch.max_kv_len
             key_tiles = -(-longest // 32) + 1
             groups = batch.num_decode * -(-(-(-heads // 16)) // 2)
-            chunks = max(1, min(key_tiles // 2, 2 * self.sm_count(q.device) // groups))
+            # chunks of at least four key tiles, at most 32 of them (the merge kernel's lanes)
+            chunks = max(1, min(key_tiles // 4, 2 * self.sm_count(q.device) // groups, 32))
             partial = None
             if chunks > 1:
                 partial = torch.empty(batch.num_decode * chunks * heads * (rank + 2), dtype=torch.float32, device=q.device)

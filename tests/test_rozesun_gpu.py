@@ -368,3 +368,22 @@ def test_per_head_products_against_the_formula(rows):
         want = torch.einsum("rhc,hvc->rhv", mixed.double().view(rows, heads, rank), w_uv.double().view(heads, vdim, rank))
         want = want * (torch.sigmoid(gate.double())[:, :, None] if per_head else torch.sigmoid(gate.double()).view(rows, heads, vdim))
         assert float((got.view(rows, heads, vdim) - want).abs().max()) < 2e-2 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("rows", [1, 8, 40, 130, 700])
+@pytest.mark.parametrize("inner,width", [(256, 128), (1216, 896)])
+def test_clamped_gate_product(rows, inner, width):
+    """min(x Wg^T, c) * sigmoid(1.702 .) * (clamp(x Wu^T, -c, c) + 1) from the many-rows product's own
+    epilogue and from the separate kernel behind the few-rows product, against the formula."""
+    from mini_llm_runtime_b200 import ops
+
+    generator = torch.Generator().manual_seed(rows + inner)
+    x = torch.randn(rows, width, generator=generator).to(torch.bfloat16)
+    gate = (torch.randn(inner, width, generator=generator) / width ** 0.5 * 2).to(torch.bfloat16)
+    up = (torch.randn(inner, width, generator=generator) / width ** 0.5 * 2).to(torch.bfloat16)
+    stacked = torch.cat([gate.view(-1, 64, width), up.view(-1, 64, width)], dim=1).reshape(2 * inner, width)
+    got = ops.current().linear_clamped_gate(x.to(DEVICE), stacked.to(DEVICE).contiguous(), 64, 1.3, 1.702)
+    g = (x.double() @ gate.double().T).clamp(max=1.3)
+    u = (x.double() @ up.double().T).clamp(-1.3, 1.3)
+    want = g * torch.sigmoid(1.702 * g) * (u + 1)
+    assert float((got.double().cpu() - want).abs().max()) < 2e-2 * float(want.abs().max())
