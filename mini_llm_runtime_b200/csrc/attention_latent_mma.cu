@@ -33,28 +33,39 @@ struct LatentMmaArgs {
   int table_width, heads, rank, rot, page_size, window;
   float scale_log2;
   const float* sink;
+  int stages;                // key tiles in shared memory (2 .. 4): stages - 1 of them are on their way while one is used
   const int* decode_seg;     // decoded rows: the segments to take (null: segments 0, 1, ..)
   float* partial;            // decoded rows in several chunks: [item][chunk][head][rank + 2]
 };
 
-// Keys key0 .. key0 + 31 into a tile: each warp takes rows in turn, looks the row's page up once and its
-// lanes copy the row's 16-byte pieces.  Keys outside [key_lo, key_hi] or on pages the request does not
-// hold become zeros.
+// Keys key0 .. key0 + 31 into a tile.  Lane l of every warp looks up the page of key key0 + l (32 keys,
+// 32 lanes: all lookups of a tile are in flight together; one lookup after the other cost eight
+// round trips per tile and warp); then each warp takes rows in turn and its lanes copy the row's 16-byte
+// pieces.  Keys outside [key_lo, key_hi] or on pages the request does not hold become zeros.
 __device__ __forceinline__ void load_key_tile(bf16* tile, int stride, const bf16* pool, const int* __restrict__ table,
                                               int key0, int key_lo, int key_hi, int page_size, int dk) {
   const int chunks = dk >> 3, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  for (int r = threadIdx.x >> 5; r < LM_KEYS; r += warps) {
-    const int key = key0 + r;
-    bool valid = key >= key_lo && key <= key_hi;
-    const bf16* src = pool;
-    if (valid) {
+  long long my_row = -1;       // row of the pool that holds key key0 + lane
+  {
+    const int key = key0 + lane;
+    if (key >= key_lo && key <= key_hi) {
       const int logical = key / page_size;
       const int page = table[logical];
-      valid = page >= 0;
-      if (valid) src = pool + ((size_t)page * page_size + (key - logical * page_size)) * dk;
+      if (page >= 0) my_row = (long long)page * page_size + (key - logical * page_size);
     }
-    for (int c = lane; c < chunks; c += 32) cp_async_16(tile + r * stride + c * 8, valid ? src + c * 8 : pool, valid);
   }
+  for (int r = threadIdx.x >> 5; r < LM_KEYS; r += warps) {
+    const long long row = __shfl_sync(0xffffffffu, my_row, r);
+    const bool valid = row >= 0;
+    const bf16* src = pool + (valid ? row : 0) * dk;
+    for (int c = lane; c < chunks; c += 32) cp_async_16(tile + r * stride + c * 8, src + c * 8, valid);
+  }
+}
+
+__device__ __forceinline__ void cp_async_wait_pending(int pending) {
+  if (pending <= 0) cp_async_wait<0>();
+  else if (pending == 1) cp_async_wait<1>();
+  else cp_async_wait<2>();
 }
 
 template <int G, bool DECODE>
@@ -67,8 +78,8 @@ latent_mma_kernel(const bf16* q, const bf16* pool, float* __restrict__ out, cons
   extern __shared__ __align__(128) uint8_t latent_shared[];
   const int DK = p.rank + p.rot, S = DK + 8;          // padded row stride: S / 8 is odd, ldmatrix is conflict-free
   bf16* q_tile = reinterpret_cast<bf16*>(latent_shared);                 // [G groups][16][S]
-  bf16* k_tiles = q_tile + G * LM_TOKENS * S;                            // 2 x [32][S]
-  bf16* p_tile = k_tiles + 2 * LM_KEYS * S;                              // [G][16][LM_P_STRIDE]
+  bf16* k_tiles = q_tile + G * LM_TOKENS * S;                            // stages x [32][S]
+  bf16* p_tile = k_tiles + p.stages * LM_KEYS * S;                       // [G][16][LM_P_STRIDE]
   float* stat_max = reinterpret_cast<float*>(p_tile + G * LM_TOKENS * LM_P_STRIDE);   // [G][4][16]
   float* stat_sum = stat_max + G * LM_SPLIT * LM_TOKENS;                              // [G][4][16]
 
@@ -103,8 +114,12 @@ latent_mma_kernel(const bf16* q, const bf16* pool, float* __restrict__ out, cons
     const bf16* src = valid ? q + ((size_t)(q_start + row0 + (DECODE ? 0 : t)) * p.heads + h) * DK + c * 8 : q;
     cp_async_16(q_tile + r * S + c * 8, src, valid);
   }
-  load_key_tile(k_tiles, S, pool, table, first_tile, lowest_key, last_key, p.page_size, DK);
-  cp_async_commit();
+  // the first stages - 1 key tiles are asked for at once (the queries travel with the first)
+  for (int i = 0; i < p.stages - 1; ++i) {
+    if (first_tile + i * LM_KEYS <= last_key)
+      load_key_tile(k_tiles + i * LM_KEYS * S, S, pool, table, first_tile + i * LM_KEYS, lowest_key, last_key, p.page_size, DK);
+    cp_async_commit();
+  }
 
   // this warp's value column blocks of 8: [nt_lo, nt_hi)
   const int nt_total = p.rank >> 3;
@@ -121,14 +136,17 @@ latent_mma_kernel(const bf16* q, const bf16* pool, float* __restrict__ out, cons
   float* sum_mine = stat_sum + group * LM_SPLIT * LM_TOKENS;
 
   int buffer = 0;
-  for (int k0 = first_tile; k0 <= last_key; k0 += LM_KEYS, buffer ^= 1) {
-    cp_async_wait<0>();
+  for (int k0 = first_tile; k0 <= last_key; k0 += LM_KEYS, buffer = buffer + 1 == p.stages ? 0 : buffer + 1) {
+    cp_async_wait_pending(p.stages - 2);
     __syncthreads();
-    if (k0 + LM_KEYS <= last_key) {
-      load_key_tile(k_tiles + (buffer ^ 1) * LM_KEYS * S, S, pool, table, k0 + LM_KEYS, lowest_key, last_key,
-                    p.page_size, DK);
+    {
+      // the tile stages - 1 ahead goes where the tile before this one lay
+      const int ahead = k0 + (p.stages - 1) * LM_KEYS;
+      const int into = buffer == 0 ? p.stages - 1 : buffer - 1;
+      if (ahead <= last_key)
+        load_key_tile(k_tiles + into * LM_KEYS * S, S, pool, table, ahead, lowest_key, last_key, p.page_size, DK);
+      cp_async_commit();
     }
-    cp_async_commit();
     const bf16* k_tile = k_tiles + buffer * LM_KEYS * S;
 
     // scores of this warp's 8 keys; two chains of sums, over the even and the odd 16-channel steps
@@ -262,47 +280,42 @@ latent_mma_kernel(const bf16* q, const bf16* pool, float* __restrict__ out, cons
   }
 }
 
-// Chunks of a decoded row merged in chunk order: one warp per (item, head).
+// Chunks of a decoded row merged: one CTA per (item, head).  Warp 0 turns the chunks' maxima and
+// denominators into one factor per chunk; then every thread sums its four columns over the chunks in
+// chunk order, eight chunks' loads in flight at a time.
 __global__ void __launch_bounds__(128)
 latent_merge_kernel(const float* partial, float* __restrict__ out, const int* __restrict__ decode_seg,
                     const int* __restrict__ seg_q_start, const float* __restrict__ sink, int items, int chunks, int heads,
                     int rank) {
   pdl_trigger();
-  pdl_wait();
-  const int lane = threadIdx.x & 31;
-  const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (unit >= (long long)items * heads) return;
-  const int item = (int)(unit / heads), head = (int)(unit - (long long)item * heads);
+  __shared__ float factor[32];
+  const int item = blockIdx.x / heads, head = blockIdx.x - item * heads;
   const int seg = decode_seg != nullptr ? decode_seg[item] : item;
+  const int lane = threadIdx.x & 31;
+  pdl_wait();
   const float* mine = partial + ((size_t)item * chunks * heads + head) * (rank + 2);
   const size_t step = (size_t)heads * (rank + 2);
-  // lane c holds chunk c's maximum and denominator (at most 32 chunks), so that all of them are asked for at once
-  const float sink_log2 = sink != nullptr ? sink[head] * 1.4426950408889634f : -INFINITY;
-  const float my_max = lane < chunks ? __ldcg(mine + lane * step + rank) : -INFINITY;
-  const float my_sum = lane < chunks ? __ldcg(mine + lane * step + rank + 1) : 0.f;
-  const float top = fmaxf(warp_max(my_max), sink_log2);
-  const float my_factor = my_max == -INFINITY ? 0.f : exp2f(my_max - top);
-  float total = warp_sum(my_sum * my_factor);
-  if (sink != nullptr) total += exp2f(sink_log2 - top);
-  float sums[LM_SPLIT * LM_MAX_NT * 8 / 32];
-#pragma unroll
-  for (int j = 0; j < LM_SPLIT * LM_MAX_NT * 8 / 32; ++j) sums[j] = 0.f;
-#pragma unroll 4
-  for (int c = 0; c < chunks; ++c) {
-    const float* theirs = mine + c * step;
-    const float f = __shfl_sync(0xffffffffu, my_factor, c);
-#pragma unroll
-    for (int j = 0; j < LM_SPLIT * LM_MAX_NT * 8 / 32; ++j) {
-      const int d = lane + 32 * j;
-      if (d < rank) sums[j] = fmaf(__ldcg(theirs + d), f, sums[j]);
-    }
+  if (threadIdx.x < 32) {
+    const float sink_log2 = sink != nullptr ? sink[head] * 1.4426950408889634f : -INFINITY;
+    const float my_max = lane < chunks ? __ldcg(mine + lane * step + rank) : -INFINITY;
+    const float my_sum = lane < chunks ? __ldcg(mine + lane * step + rank + 1) : 0.f;
+    const float top = fmaxf(warp_max(my_max), sink_log2);
+    const float my_factor = my_max == -INFINITY ? 0.f : exp2f(my_max - top);
+    float total = warp_sum(my_sum * my_factor);
+    if (sink != nullptr) total += exp2f(sink_log2 - top);
+    factor[lane] = my_factor / total;
   }
-  const float inv = 1.f / total;
+  __syncthreads();
   float* dst = out + ((size_t)seg_q_start[seg] * heads + head) * rank;
-#pragma unroll
-  for (int j = 0; j < LM_SPLIT * LM_MAX_NT * 8 / 32; ++j) {
-    const int d = lane + 32 * j;
-    if (d < rank) dst[d] = sums[j] * inv;
+  for (int d = threadIdx.x * 2; d < rank; d += 256) {       // rank + 2 is even: pairs of columns are 8-byte aligned
+    float2 sum = make_float2(0.f, 0.f);
+#pragma unroll 8
+    for (int c = 0; c < chunks; ++c) {
+      const float2 v = __ldcg(reinterpret_cast<const float2*>(mine + c * step + d));
+      sum.x = fmaf(v.x, factor[c], sum.x);
+      sum.y = fmaf(v.y, factor[c], sum.y);
+    }
+    *reinterpret_cast<float2*>(dst + d) = sum;
   }
 }
 
@@ -440,8 +453,8 @@ using namespace mlr;
 
 MLR_DEFINE_PDL_SWITCH
 
-static size_t latent_mma_shared(int groups, int dk) {
-  return sizeof(bf16) * ((size_t)(groups * LM_TOKENS + 2 * LM_KEYS) * (dk + 8) + groups * LM_TOKENS * LM_P_STRIDE) +
+static size_t latent_mma_shared(int groups, int dk, int stages = 2) {
+  return sizeof(bf16) * ((size_t)(groups * LM_TOKENS + stages * LM_KEYS) * (dk + 8) + groups * LM_TOKENS * LM_P_STRIDE) +
          sizeof(float) * 2 * groups * LM_SPLIT * LM_TOKENS;
 }
 
@@ -455,7 +468,7 @@ MLR_EXPORT int mlr_latent_attention_mma_fits(int rank, int rot) {
 template <int G, bool DECODE>
 static int latent_mma_launch(const void* q, const void* pool, float* out, const int* tile_seg, const int* tile_row0,
                              dim3 grid, const LatentMmaArgs& args, cudaStream_t stream) {
-  const size_t shared = latent_mma_shared(G, args.rank + args.rot);
+  const size_t shared = latent_mma_shared(G, args.rank + args.rot, args.stages);
   if (shared > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(latent_mma_kernel<G, DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (err != cudaSuccess) return (int)err;
@@ -475,7 +488,7 @@ static int latent_mma_args(LatentMmaArgs& args, const void* q, const void* pool,
   args.seg_q_start = seg_q_start; args.seg_q_len = seg_q_len; args.seg_pos0 = seg_pos0; args.block_table = block_table;
   args.seg_slot = seg_slot; args.table_width = table_width; args.heads = heads; args.rank = rank; args.rot = rot;
   args.page_size = page_size; args.window = window; args.scale_log2 = scale * 1.4426950408889634f; args.sink = sink;
-  args.decode_seg = nullptr; args.partial = nullptr;
+  args.decode_seg = nullptr; args.partial = nullptr; args.stages = 2;
   return MLR_OK;
 }
 
@@ -523,13 +536,14 @@ MLR_EXPORT int mlr_latent_attention_mma_decode(const void* q, const void* pool, 
   args.decode_seg = decode_seg;
   args.partial = partial;
   const int blocks16 = (heads + LM_TOKENS - 1) / LM_TOKENS;
+  // a decoded row's CTAs are few and wait for memory: as many key tiles on their way as fit (up to three)
+  while (args.stages < 4 && latent_mma_shared(blocks16 == 1 ? 1 : 2, rank + rot, args.stages + 1) <= 160 * 1024) ++args.stages;
   if (blocks16 == 1)
     status = latent_mma_launch<1, true>(q, pool, out, nullptr, nullptr, dim3(count, 1, chunks), args, stream);
   else
     status = latent_mma_launch<2, true>(q, pool, out, nullptr, nullptr, dim3(count, (blocks16 + 1) / 2, chunks), args, stream);
   if (status != MLR_OK || chunks == 1) return status;
-  const long long units = (long long)count * heads;
-  launch_kernel(latent_merge_kernel, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, stream, (const float*)partial, out,
+  launch_kernel(latent_merge_kernel, dim3((unsigned)(count * heads)), dim3(128), 0, stream, (const float*)partial, out,
                 decode_seg, seg_q_start, sink, count, chunks, heads, rank);
   return launch_status();
 }

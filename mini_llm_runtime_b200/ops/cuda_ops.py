@@ -1170,6 +1170,7 @@ class CudaOps:
                                  gate_per_head=gate_per_head)
 
     use_latent_decode_kernel = True
+    latent_decode_chunk_tiles = 4      # key tiles (of 32 keys) a CTA of the decode attention takes at least
 
     def latent_attention(self, q: torch.Tensor, pool: torch.Tensor, batch: AttentionBatch, heads: int, rank: int,
                          rot: int, scale: float, window: int, sink: torch.Tensor | None) -> torch.Tensor:
@@ -1200,8 +1201,8 @@ class CudaOps:
             longest = min(batch.max_kv_len, window + 31) if window else batch.max_kv_len
             key_tiles = -(-longest // 32) + 1
             groups = batch.num_decode * -(-(-(-heads // 16)) // 2)
-            # chunks of at least four key tiles, at most 32 of them (the merge kernel's lanes)
-            chunks = max(1, min(key_tiles // 4, 2 * self.sm_count(q.device) // groups, 32))
+            # chunks of at least ``latent_decode_chunk_tiles`` key tiles, at most 32 of them (the merge kernel's lanes)
+            chunks = max(1, min(key_tiles // self.latent_decode_chunk_tiles, 2 * self.sm_count(q.device) // groups, 32))
             partial = None
             if chunks > 1:
                 partial = torch.empty(batch.num_decode * chunks * heads * (rank + 2), dtype=torch.float32, device=q.device)
