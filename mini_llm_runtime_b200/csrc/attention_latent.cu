@@ -52,25 +52,31 @@ latent_prepare_kernel(const float* down, long long down_stride, int q_at, int q_
   pdl_trigger();
   __shared__ float scratch[32];
   const int row = blockIdx.x;
+  // what does not depend on the product is asked for before the wait: the row's place and position, and
+  // (into the L2) the norms' weights and the frequencies; both sums of squares are then taken in one
+  // sweep, so that the kernel waits for memory three times instead of six
+  const long long slot = write ? slots[row] : -1;
+  const float position = (float)positions[row];
+  for (int d = threadIdx.x * 32; d < q_rank; d += blockDim.x * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(q_weight + d));
+  for (int d = threadIdx.x * 32; d < rank; d += blockDim.x * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(c_weight + d));
+  if (threadIdx.x * 32 < pairs) asm volatile("prefetch.global.L2 [%0];" ::"l"(frequencies + threadIdx.x * 32));
   pdl_wait();
   const float* in = down + (size_t)row * down_stride;
+  const bool store = write && slot >= 0;
+  float sq_q = 0.f, sq_c = 0.f;
+  for (int d = threadIdx.x; d < q_rank; d += blockDim.x) sq_q = fmaf(in[q_at + d], in[q_at + d], sq_q);
+  if (store)
+    for (int d = threadIdx.x; d < rank; d += blockDim.x) sq_c = fmaf(in[c_at + d], in[c_at + d], sq_c);
   {
-    float sq = 0.f;
-    for (int d = threadIdx.x; d < q_rank; d += blockDim.x) sq = fmaf(in[q_at + d], in[q_at + d], sq);
-    const float factor = 1.f / sqrtf(block_sum(sq, scratch) / (float)q_rank + eps);
+    const float factor = 1.f / sqrtf(block_sum(sq_q, scratch) / (float)q_rank + eps);
     T* dst = q_latent + (size_t)row * q_rank;
     for (int d = threadIdx.x; d < q_rank; d += blockDim.x) dst[d] = from_float<T>(in[q_at + d] * factor * q_weight[d]);
   }
-  if (!write) return;
-  const long long slot = slots[row];
-  if (slot < 0) return;
+  if (!store) return;
   T* dst = pool + (size_t)slot * (rank + rot);
-  float sq = 0.f;
-  for (int d = threadIdx.x; d < rank; d += blockDim.x) sq = fmaf(in[c_at + d], in[c_at + d], sq);
-  const float factor = 1.f / sqrtf(block_sum(sq, scratch) / (float)rank + eps);
+  const float factor = 1.f / sqrtf(block_sum(sq_c, scratch) / (float)rank + eps);
   for (int d = threadIdx.x; d < rank; d += blockDim.x) dst[d] = from_float<T>(in[c_at + d] * factor * c_weight[d]);
   const float* r = in + c_at + rank;
-  const float position = (float)positions[row];
   for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
     int a, b;
     pair_places(i, pairs, interleaved, &a, &b);

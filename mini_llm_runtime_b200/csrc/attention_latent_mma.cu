@@ -356,37 +356,59 @@ head_linear_mma_kernel(const bf16* __restrict__ w, TO* __restrict__ y, HeadMmaAr
 #pragma unroll
   for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
   pdl_wait();
-  for (int k0 = 0; k0 < p.K; k0 += HM_K) {
-    // x: rows x HM_K floats as float4 pieces, rounded to bfloat16
-    for (int item = threadIdx.x; item < HM_ROWS * HM_K / 4; item += 128) {
+  // the pieces of the next k step are fetched into registers while the products of this one run
+  constexpr int A_PIECES = HM_ROWS * HM_K / 4 / 128, B_PIECES = HM_COLS * HM_K / 8 / 128;
+  float4 a_next[A_PIECES];
+  uint4 b_next[B_PIECES];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < A_PIECES; ++i) {
+      const int item = threadIdx.x + 128 * i;
       const int r = item / (HM_K / 4), c = item - r * (HM_K / 4);
       const int row = row0 + r, k = k0 + 4 * c;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      a_next[i] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (row < p.rows && k < p.K)
-        v = __ldcg(reinterpret_cast<const float4*>(p.x + (size_t)row * p.x_row + (size_t)head * p.x_head + k));
+        a_next[i] = __ldcg(reinterpret_cast<const float4*>(p.x + (size_t)row * p.x_row + (size_t)head * p.x_head + k));
+    }
+#pragma unroll
+    for (int i = 0; i < B_PIECES; ++i) {
+      const int item = threadIdx.x + 128 * i;
+      b_next[i] = make_uint4(0, 0, 0, 0);
+      if (p.kn) {
+        const int k = item / (HM_COLS / 8), c = item - k * (HM_COLS / 8);
+        if (k0 + k < p.K && n0 + 8 * c < p.N)
+          b_next[i] = *reinterpret_cast<const uint4*>(wh + (size_t)(k0 + k) * p.N + n0 + 8 * c);
+      } else {
+        const int n = item / (HM_K / 8), c = item - n * (HM_K / 8);
+        if (n0 + n < p.N && k0 + 8 * c < p.K)
+          b_next[i] = *reinterpret_cast<const uint4*>(wh + (size_t)(n0 + n) * p.K + k0 + 8 * c);
+      }
+    }
+  };
+  fetch(0);
+  for (int k0 = 0; k0 < p.K; k0 += HM_K) {
+#pragma unroll
+    for (int i = 0; i < A_PIECES; ++i) {
+      const int item = threadIdx.x + 128 * i;
+      const int r = item / (HM_K / 4), c = item - r * (HM_K / 4);
       uint2 packed;
-      packed.x = pack_bf16(v.x, v.y);
-      packed.y = pack_bf16(v.z, v.w);
+      packed.x = pack_bf16(a_next[i].x, a_next[i].y);
+      packed.y = pack_bf16(a_next[i].z, a_next[i].w);
       *reinterpret_cast<uint2*>(a_tile + r * AS + 4 * c) = packed;
     }
-    if (p.kn) {
-      for (int item = threadIdx.x; item < HM_K * HM_COLS / 8; item += 128) {
+#pragma unroll
+    for (int i = 0; i < B_PIECES; ++i) {
+      const int item = threadIdx.x + 128 * i;
+      if (p.kn) {
         const int k = item / (HM_COLS / 8), c = item - k * (HM_COLS / 8);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (k0 + k < p.K && n0 + 8 * c < p.N)
-          v = *reinterpret_cast<const uint4*>(wh + (size_t)(k0 + k) * p.N + n0 + 8 * c);
-        *reinterpret_cast<uint4*>(b_tile + k * BS_KN + 8 * c) = v;
-      }
-    } else {
-      for (int item = threadIdx.x; item < HM_COLS * HM_K / 8; item += 128) {
+        *reinterpret_cast<uint4*>(b_tile + k * BS_KN + 8 * c) = b_next[i];
+      } else {
         const int n = item / (HM_K / 8), c = item - n * (HM_K / 8);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (n0 + n < p.N && k0 + 8 * c < p.K)
-          v = *reinterpret_cast<const uint4*>(wh + (size_t)(n0 + n) * p.K + k0 + 8 * c);
-        *reinterpret_cast<uint4*>(b_tile + n * BS_NK + 8 * c) = v;
+        *reinterpret_cast<uint4*>(b_tile + n * BS_NK + 8 * c) = b_next[i];
       }
     }
     __syncthreads();
+    if (k0 + HM_K < p.K) fetch(k0 + HM_K);
 #pragma unroll
     for (int kk = 0; kk < HM_K / 16; ++kk) {
       uint32_t a[4];
