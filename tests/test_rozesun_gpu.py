@@ -317,7 +317,7 @@ def _attention_case(lengths, positions, heads, rank, rot, page=16, seed=0):
     return q, pool, batch
 
 
-@pytest.mark.parametrize("heads,rank,rot,window,sink", [(3, 40, 8, 0, False), (2, 96, 32, 37, True), (18, 64, 16, 100, True),
+@pytest.mark.parametrize("heads,rank,rot,window,sink", [(3, 40, 8, 0, False), (2, 88, 24, 37, True), (18, 64, 16, 100, True),
                                                          (16, 512, 64, 0, False), (1, 24, 8, 9, True)])
 def test_tensor_core_attention_against_the_float32_kernel(heads, rank, rot, window, sink):
     """Prompt portions beside decoded rows (some in several key chunks) on the tensor-core kernels
