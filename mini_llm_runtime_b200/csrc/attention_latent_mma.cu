@@ -86,8 +86,11 @@ latent_mma_kernel(const bf16* q, const bf16* pool, float* __restrict__ out, cons
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int group = warp / LM_SPLIT, split = warp % LM_SPLIT;
   // prompt tile: a group is one head, its rows 16 tokens; decoded row: a group is 16 heads of the one token
-  const int seg = DECODE ? (p.decode_seg != nullptr ? p.decode_seg[blockIdx.x] : blockIdx.x) : tile_seg[blockIdx.x];
-  const int row0 = DECODE ? 0 : tile_row0[blockIdx.x];
+  // prompt tiles are taken from the end of the list: within a portion the later rows walk more keys, and the
+  // CTAs that run longest should start first
+  const int listed = DECODE ? blockIdx.x : gridDim.x - 1 - blockIdx.x;
+  const int seg = DECODE ? (p.decode_seg != nullptr ? p.decode_seg[listed] : listed) : tile_seg[listed];
+  const int row0 = DECODE ? 0 : tile_row0[listed];
   const int head = DECODE ? (blockIdx.y * G + group) * LM_TOKENS : blockIdx.y * G + group;    // the group's (first) head
   const bool live = head < p.heads;
   const int q_start = p.seg_q_start[seg], pos0 = p.seg_pos0[seg];
