@@ -201,3 +201,29 @@ def dominant_key_case(kind, window, length, query, key, seed):
         "l0.mix.uk": lambda t: torch.cat([eye, eye]), "l0.mix.uq": query_up,
     }
     return cfg, overrides
+
+
+def random_config(seed):
+    """A configuration drawn from a seed: layer kinds in any order, sizes of every parity, a loop
+    anywhere (or none), layers with and without a feed-forward."""
+    import random
+
+    rng = random.Random(seed)
+    count = rng.randint(2, 5)
+    layers = []
+    for _ in range(count):
+        heads, dim, rot_dim = rng.randint(1, 9), rng.choice([4, 6, 8, 10, 16, 24]), rng.choice([2, 4, 8, 12, 16])
+        vdim, kv_rank, q_rank = rng.choice([3, 8, 12, 16, 20]), rng.choice([8, 12, 16, 24, 40, 72]), rng.choice([5, 8, 16, 28])
+        ff = rng.choice([0, 24, 40, 64])
+        options = dict(base=rng.choice([30.0, 1000.0, 50000.0]), scale=rng.choice([None, 0.2, 0.4]),
+                       dims=rng.choice([None, rot_dim, max(2, rot_dim - 2)]), ff=ff, limit=rng.choice([0.5, 1.0, 3.0]))
+        if rng.random() < 0.5:
+            layers.append(latent2(heads, dim, rot_dim, vdim, kv_rank, q_rank, rng.choice([1, 3, 16, 17, 40, 200]), **options))
+        else:
+            layers.append(latent(heads, dim, rot_dim, vdim, kv_rank, q_rank, **options))
+    loop = None
+    if rng.random() < 0.7:
+        start = rng.randint(0, count - 1)
+        loop = (start, rng.randint(start + 1, count), rng.randint(1, 3))
+    return config(layers, width=rng.choice([24, 36, 64, 72]), vocab=rng.choice([31, 64, 100]), loop=loop,
+                  eps=rng.choice([1e-6, 1e-5, 1e-3]), logit_scale=rng.choice([0.5, 1.0, 2.5]))

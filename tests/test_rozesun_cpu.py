@@ -171,3 +171,14 @@ def test_greedy_generation_through_the_scheduler():
         for _ in range(6):
             sequence.append(int(torch.argmax(parts.plain(sequence)[-1])))
         assert got == sequence[len(prompt):]
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_configurations_drawn_at_random(seed):
+    config = rs.random_config(seed)
+    with ops.use(FakeOps()):
+        engine = rs.REngine(config, F32, "cpu", seed=seed, num_pages=40)
+        prompts = {"a": rs.tokens_for(config["vocab"], 45, seed), "b": rs.tokens_for(config["vocab"], 21, seed + 50)}
+        got = engine.run_plan(prompts, [{"a": 17, "b": 1}, {"a": 1, "b": 2}, {"a": 2, "b": 18}, {"a": 25}])
+    for name, tokens in prompts.items():
+        rs.assert_logits_close(got[name], engine.plain(tokens), F32, f"seed {seed} {name}")

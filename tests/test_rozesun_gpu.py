@@ -387,3 +387,15 @@ def test_clamped_gate_product(rows, inner, width):
     u = (x.double() @ up.double().T).clamp(-1.3, 1.3)
     want = g * torch.sigmoid(1.702 * g) * (u + 1)
     assert float((got.double().cpu() - want).abs().max()) < 2e-2 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(seed, dtype):
+    """Layer kinds in any order, sizes of every parity, loops anywhere: a mixed batch and single tokens."""
+    config = rs.random_config(seed)
+    engine = rs.REngine(config, dtype, DEVICE, seed=seed, num_pages=40)
+    prompts = {"a": rs.tokens_for(config["vocab"], 45, seed), "b": rs.tokens_for(config["vocab"], 21, seed + 50)}
+    got = engine.run_plan(prompts, [{"a": 17, "b": 1}, {"a": 1, "b": 2}, {"a": 2, "b": 18}, {"a": 25}])
+    for name, tokens in prompts.items():
+        rs.assert_logits_close(got[name], engine.plain(tokens), dtype, f"seed {seed} {name}")
